@@ -3,7 +3,8 @@
 Cache entries (one per schedule entry that writes keys and values) with the same
 need (heads, head size, window) form a *group* with storage of its own:
 
-    k, v : [entries, pages, kv_heads, page_size, head_dim]
+    k : [entries, pages, kv_heads, page_size, head_dim]
+    v : [entries, pages, kv_heads, page_size, v_head_dim]      (v_head_dim = head_dim unless the need says otherwise)
 
 so that a (page, head) block is ``page_size * head_dim`` contiguous elements: one
 TMA box or a run of 16-byte loads for attention.  A sequence's pages are listed in
@@ -86,9 +87,10 @@ class SequenceCache:
                 n_pages = 1 + round_up(max_tokens, PAGE_SIZE) // PAGE_SIZE
             pages = GroupPages(n_pages, PAGE_SIZE, ring, name=f"cache group {index}")
             shape = (len(ids), n_pages, need.n_kv_heads, PAGE_SIZE, need.head_dim)
+            v_shape = shape[:-1] + (need.v_head_dim or need.head_dim,)
             group = CacheGroup(need, ids, pages,
                                torch.zeros(shape, dtype=dtype, device=device),
-                               torch.zeros(shape, dtype=dtype, device=device))
+                               torch.zeros(v_shape, dtype=dtype, device=device))
             self.groups.append(group)
             for position, cache_id in enumerate(ids):
                 self.group_of[cache_id] = (index, position)
@@ -147,5 +149,5 @@ class SequenceCache:
                           self.page_size, group.ring_tokens, writes)
 
     def bytes(self) -> int:
-        return sum(g.k.numel() * g.k.element_size() * 2 for g in self.groups) + \
+        return sum((g.k.numel() + g.v.numel()) * g.k.element_size() for g in self.groups) + \
             sum(a.numel() * a.element_size() for a in self.state.values())

@@ -37,8 +37,11 @@ def architecture_named(name: str) -> Architecture:
 
 def architecture_of(raw: dict) -> Architecture:
     names = raw.get("architectures")
+    if names is None and isinstance(raw.get("architecture"), str):
+        return architecture_named(raw["architecture"])          # files that name one architecture as a string
     if not isinstance(names, list) or not names or not isinstance(names[0], str):
-        raise ConfigError("config.json: 'architectures' must be a list holding the model class name")
+        raise ConfigError("config.json: 'architectures' must be a list holding the model class name "
+                          "(or 'architecture' its name)")
     return architecture_named(names[0])
 
 

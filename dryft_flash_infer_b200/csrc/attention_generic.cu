@@ -1,5 +1,7 @@
-// Causal grouped-query attention over the paged cache for any head size (multiples of 8
-// up to 256) and either storage type, written with plain loads and float32 arithmetic.
+// Causal grouped-query attention over the paged cache for any head size up to 256 (16-byte loads when
+// the key size allows them, element by element otherwise), a value size of its own, and either storage
+// type, written with plain loads and float32 arithmetic.  Optionally every head's output is multiplied
+// by sigmoid(gate[row, head]) and by a constant before it is stored.
 // It serves the float32 path of the whole model and every shape the tensor-core kernels
 // refuse.  One warp owns one (query row, query head); keys are taken 32 at a time, one per
 // lane, with the online softmax of the reference's split kernel
@@ -12,13 +14,14 @@ namespace dfi {
 constexpr int kGenericWarps = 4;
 constexpr int kMaxHeadDim = 256;
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__ out,
                                          int out_row_stride, const T* __restrict__ k_cache,
                                          const T* __restrict__ v_cache, const int* __restrict__ block_table,
                                          int table_width, const int* __restrict__ row_seq,
-                                         const int* __restrict__ row_pos, int n_q, int n_kv, int D, int page_size,
-                                         int ring_tokens, int window, float scale) {
+                                         const int* __restrict__ row_pos, int n_q, int n_kv, int D, int DV, int page_size,
+                                         int ring_tokens, int window, float scale,
+                                         const T* __restrict__ gate, int gate_row_stride, float out_scale) {
     pdl_launch_next();
     pdl_wait();
     __shared__ float q_s[kGenericWarps][kMaxHeadDim];
@@ -44,19 +47,23 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_row_stri
     for (int base = first; base <= pos; base += 32) {
         const int key = base + lane;
         const bool live = key <= pos;
-        unsigned long long offset = 0;
+        unsigned long long offset = 0;     // of the key's (page, head, place), in tokens
         float s = -INFINITY;
         if (live) {
             const int place = place_of(key, ring_tokens);
             const int page = table[place / page_size];
-            offset = (((unsigned long long)page * n_kv + kv_head) * page_size + place % page_size) * D;
-            const T* kp = k_cache + offset;
+            offset = ((unsigned long long)page * n_kv + kv_head) * page_size + place % page_size;
+            const T* kp = k_cache + offset * D;
             float dot = 0.f;
-            for (int d = 0; d < D; d += n) {
-                float kv[n];
-                load16(kp + d, kv);
+            if (VEC) {
+                for (int d = 0; d < D; d += n) {
+                    float kv[n];
+                    load16(kp + d, kv);
 #pragma unroll
-                for (int e = 0; e < n; ++e) dot += q_s[warp][d + e] * kv[e];
+                    for (int e = 0; e < n; ++e) dot += q_s[warp][d + e] * kv[e];
+                }
+            } else {
+                for (int d = 0; d < D; ++d) dot += q_s[warp][d] * to_float(kp[d]);
             }
             s = dot;
         }
@@ -71,20 +78,21 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_row_stri
         for (int kk = 0; kk < count; ++kk) {
             const float pk = __shfl_sync(0xffffffffu, p, kk);
             const unsigned long long off = __shfl_sync(0xffffffffu, offset, kk);
-            const T* vp = v_cache + off;
+            const T* vp = v_cache + off * DV;
 #pragma unroll
             for (int j = 0; j < kMaxHeadDim / 32; ++j) {
                 const int d = lane + 32 * j;
-                if (d < D) acc[j] += pk * to_float(vp[d]);
+                if (d < DV) acc[j] += pk * to_float(vp[d]);
             }
         }
     }
-    T* o = out + (size_t)row * out_row_stride + (size_t)head * D;
-    const float inv = 1.0f / l;
+    T* o = out + (size_t)row * out_row_stride + (size_t)head * DV;
+    float inv = out_scale / l;
+    if (gate != nullptr) inv /= 1.f + expf(-to_float(gate[(size_t)row * gate_row_stride + head]));
 #pragma unroll
     for (int j = 0; j < kMaxHeadDim / 32; ++j) {
         const int d = lane + 32 * j;
-        if (d < D) o[d] = from_float<T>(acc[j] * inv);
+        if (d < DV) o[d] = from_float<T>(acc[j] * inv);
     }
 }
 
@@ -93,32 +101,34 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, int q_row_stri
 using namespace dfi;
 
 // q [rows, q_row_stride] holds n_q heads of head_dim per row (already normalised and
-// rotated); out [rows, out_row_stride].  row_seq gives each row's line of block_table and
+// rotated); out [rows, out_row_stride] holds n_q heads of v_dim (the size of a cached value).
+// gate (or null) [rows, gate_row_stride] holds one number per row and head: the head's output is
+// multiplied by its sigmoid; out_scale multiplies every output.  row_seq gives each row's line of block_table and
 // row_pos its absolute position; the cache already holds the keys up to that position.
 DFI_EXPORT int dfi_attention_generic(const void* q, int q_row_stride, void* out, int out_row_stride,
                                      const void* k_cache, const void* v_cache, const int* block_table,
                                      int table_width, const int* row_seq, const int* row_pos, int rows, int n_q,
-                                     int n_kv, int head_dim, int page_size, int ring_tokens, int window,
-                                     float scale, int dtype, void* stream) {
+                                     int n_kv, int head_dim, int v_dim, int page_size, int ring_tokens, int window,
+                                     float scale, const void* gate, int gate_row_stride, float out_scale,
+                                     int dtype, void* stream) {
     if (rows <= 0) return DFI_OK;
+    if (v_dim <= 0 || v_dim > kMaxHeadDim) return DFI_ERR_SHAPE;
     if (head_dim <= 0 || head_dim > kMaxHeadDim || n_q <= 0 || n_kv <= 0 || n_q % n_kv) return DFI_ERR_SHAPE;
     if (page_size <= 0 || table_width <= 0 || window < 0 || ring_tokens < 0) return DFI_ERR_SHAPE;
-    const int vec = dtype == DFI_DTYPE_F32 ? 4 : 8;
-    if (head_dim % vec) return DFI_ERR_SHAPE;
-    if (!aligned16(k_cache) || !aligned16(v_cache)) return DFI_ERR_ALIGN;
+    const bool vec = head_dim % (dtype == DFI_DTYPE_F32 ? 4 : 8) == 0 && aligned16(k_cache);
     cudaStream_t st = (cudaStream_t)stream;
     dim3 grid(rows, (n_q + kGenericWarps - 1) / kGenericWarps);
     if (grid.y > 65535) return DFI_ERR_LIMIT;
-    if (dtype == DFI_DTYPE_F32)
-        launch(attention_generic_kernel<float>, grid, kGenericWarps * 32, 0, st, 
-            (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_cache,
-            (const float*)v_cache, block_table, table_width, row_seq, row_pos, n_q, n_kv, head_dim, page_size,
-            ring_tokens, window, scale);
-    else if (dtype == DFI_DTYPE_BF16)
-        launch(attention_generic_kernel<bf16>, grid, kGenericWarps * 32, 0, st, 
-            (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_cache,
-            (const bf16*)v_cache, block_table, table_width, row_seq, row_pos, n_q, n_kv, head_dim, page_size,
-            ring_tokens, window, scale);
+#define DFI_LAUNCH_GENERIC(T, V)                                                                                  \
+    launch(attention_generic_kernel<T, V>, grid, kGenericWarps * 32, 0, st, (const T*)q, q_row_stride, (T*)out,     \
+           out_row_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_width, row_seq, row_pos, n_q,  \
+           n_kv, head_dim, v_dim, page_size, ring_tokens, window, scale, (const T*)gate, gate_row_stride, out_scale)
+    if (dtype == DFI_DTYPE_F32) {
+        if (vec) DFI_LAUNCH_GENERIC(float, true); else DFI_LAUNCH_GENERIC(float, false);
+    } else if (dtype == DFI_DTYPE_BF16) {
+        if (vec) DFI_LAUNCH_GENERIC(bf16, true); else DFI_LAUNCH_GENERIC(bf16, false);
+    }
+#undef DFI_LAUNCH_GENERIC
     else return DFI_ERR_DTYPE;
     DFI_CHECK_LAUNCH();
     return DFI_OK;

@@ -76,6 +76,11 @@ class Engine:
             if config is not None or random_weights:
                 raise ValueError("give either a model folder, or a configuration with random_weights=True")
             self.config = load_config(model_path)
+            if hasattr(self.config, "with_tensor_shapes"):
+                # sizes that the architecture's file leaves to the shapes of its tensors
+                from ..weights.safetensors_io import ModelFiles
+                files = ModelFiles(model_path)
+                self.config = self.config.with_tensor_shapes({n: tuple(files.info(n)[1]) for n in files.names()})
         else:
             if config is None or not random_weights:
                 raise ValueError("without a model folder, give config=... and random_weights=True")

@@ -36,7 +36,8 @@ class DecoderModel:
             block_class = part_factory("block", layer.block)
             self.blocks.append(block_class(
                 build_part("mixer", layer.mixer, spec.hidden_size),
-                build_part("feed_forward", layer.feed_forward, spec.hidden_size),
+                build_part("feed_forward", layer.feed_forward, spec.hidden_size)
+                if layer.feed_forward is not None else None,
                 {name: build_part("norm", norm, spec.hidden_size) for name, norm in layer.norms.items()}))
         self.final_norm = build_part("norm", spec.final_norm, spec.hidden_size) if spec.final_norm is not None else None
         self.embedding = None   # [vocab, hidden]
@@ -84,6 +85,7 @@ class DecoderModel:
         """Creates every part's device buffers (uninitialised)."""
         self.dtype, self.device = dtype, device
         for part in self._parts():
+            part.set_compute_dtype(dtype)
             held = {}
             for name, (shape, precision) in part.buffer_shapes().items():
                 held[name] = torch.empty(shape, dtype=dtype if precision == "compute" else torch.float32,
@@ -96,8 +98,12 @@ class DecoderModel:
 
     def destination(self, expected: ExpectedTensor) -> torch.Tensor:
         """The rows of a device buffer that ``expected`` fills."""
-        buffer = self._buffers[id(expected.owner)][expected.decl.buffer]
-        return buffer[expected.decl.row_start: expected.decl.row_start + expected.decl.shape[0]]
+        decl = expected.decl
+        buffer = self._buffers[id(expected.owner)][decl.buffer]
+        rows = buffer[decl.row_start: decl.row_start + decl.rows]
+        if len(decl.shape) == 2 and decl.shape[1] != buffer.shape[1]:
+            return rows[:, decl.col_start: decl.col_start + decl.shape[1]]
+        return rows.view(decl.shape) if not decl.shape else rows
 
     def bind(self) -> None:
         for part in self._parts():
@@ -144,7 +150,9 @@ class DecoderModel:
     def _forward(self, ctx, cache) -> torch.Tensor | None:
         spec = self.spec
         ctx.decode_plans = {}       # what the kernels of this pass work out once and share between layers
-        residual = kernels.embedding(self.embedding, ctx.tokens, scale=spec.embedding_scale)
+        # the residual stream: in the engine's dtype, or float32 for architectures that sum it in 32-bit
+        residual = kernels.embedding(self.embedding, ctx.tokens, scale=spec.embedding_scale,
+                                     out_dtype=torch.float32 if spec.residual_float32 else None)
         pending = None
         schedule = self.spec.schedule
         for position, entry in enumerate(schedule):

@@ -183,11 +183,20 @@ def _f(x: float):
     return ctypes.c_float(x)
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
-    """``table[ids] * scale`` for int32 ``ids [rows]``."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0,
+              out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``table[ids] * scale`` for int32 ``ids [rows]``, in the table's dtype or, with
+    ``out_dtype=torch.float32``, widened to float32 (the start of a float32 residual stream)."""
     _need_cuda(table, ids)
     assert ids.dtype == torch.int32 and table.is_contiguous()
     rows, (vocab, hidden) = ids.numel(), table.shape
+    if out_dtype is not None and out_dtype != table.dtype:
+        if out_dtype != torch.float32:
+            raise KernelError(f"embedding: rows come in the table's dtype or float32, not {out_dtype}")
+        out = torch.empty((rows, hidden), dtype=torch.float32, device=table.device)
+        _check(_core().dfi_embedding_float(_ptr(table), _ptr(ids), _ptr(out), rows, hidden, vocab, _f(scale),
+                                           _code(table), _stream()), "embedding")
+        return out
     out = torch.empty((rows, hidden), dtype=table.dtype, device=table.device)
     _check(_core().dfi_embedding(_ptr(table), _ptr(ids), _ptr(out), rows, hidden, vocab, _code(table), _stream()),
            "embedding")
@@ -206,8 +215,61 @@ def scale_add(a: torch.Tensor, b: torch.Tensor | None, scale: float = 1.0) -> to
 
 
 def add_rows(residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
-    """``residual += delta`` in place: the residual sum where no norm follows it."""
+    """``residual += delta`` in place: the residual sum where no norm follows it.  A float32 residual
+    takes a delta of either dtype."""
+    if residual.dtype == torch.float32 and delta.dtype != torch.float32:
+        _need_cuda(residual, delta)
+        assert residual.is_contiguous() and delta.is_contiguous() and residual.shape == delta.shape
+        _check(_core().dfi_add_to_float(_ptr(residual), _ptr(delta), ctypes.c_longlong(residual.numel()), _code(delta),
+                                        _stream()), "add_rows")
+        return residual
     return scale_add(residual, delta, 1.0)
+
+
+def dynamic_tanh(residual: torch.Tensor, delta: torch.Tensor | None, alpha: torch.Tensor, weight: torch.Tensor,
+                 bias: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``tanh(alpha * x) * weight + bias`` per element of the float32 rows ``residual``, to which
+    ``delta`` (in ``out_dtype``; or None) is added in place first.  ``alpha`` is one float32 on the
+    device; the result comes in ``out_dtype``."""
+    _need_cuda(residual, delta, alpha, weight, bias)
+    if residual.dtype != torch.float32:
+        raise KernelError(f"dynamic_tanh reads a float32 residual stream, got {residual.dtype}")
+    assert residual.is_contiguous() and residual.dim() == 2 and alpha.numel() == 1
+    assert all(t.dtype == torch.float32 for t in (alpha, weight, bias))
+    assert weight.numel() == residual.shape[1] and bias.numel() == residual.shape[1]
+    assert delta is None or (delta.dtype == out_dtype and delta.shape == residual.shape and delta.is_contiguous())
+    if out_dtype not in _DTYPE_CODE:
+        raise KernelError(f"unsupported dtype {out_dtype}: kernels take float32 and bfloat16")
+    out = torch.empty(residual.shape, dtype=out_dtype, device=residual.device)
+    _check(_core().dfi_dynamic_tanh(_ptr(residual), _ptr(delta), _ptr(alpha), _ptr(weight), _ptr(bias), _ptr(out),
+                                    residual.shape[0], residual.shape[1], _DTYPE_CODE[out_dtype], _stream()),
+           "dynamic_tanh")
+    return out
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "tanh": 4}
+
+
+def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """``x = act(x)`` in place, element by element, for ``kind`` in ``ACTIVATIONS``: ``relu2`` is
+    ``relu(x)^2``, ``gelu_tanh`` is ``0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))``."""
+    _need_cuda(x)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {kind!r}; known: {', '.join(ACTIVATIONS)}")
+    assert x.is_contiguous()
+    _check(_core().dfi_activation(_ptr(x), ctypes.c_longlong(x.numel()), ACTIVATIONS[kind], _code(x), _stream()),
+           "activation")
+    return x
+
+
+def weighted_sum(a: torch.Tensor, b: torch.Tensor, scale_a: float, scale_b: float) -> torch.Tensor:
+    """``a * scale_a + b * scale_b``, element by element (float32 arithmetic, one rounding)."""
+    _need_cuda(a, b)
+    assert a.is_contiguous() and b.is_contiguous() and a.shape == b.shape and a.dtype == b.dtype
+    out = torch.empty_like(a)
+    _check(_core().dfi_weighted_sum(_ptr(a), _ptr(b), _ptr(out), ctypes.c_longlong(a.numel()), _f(scale_a),
+                                    _f(scale_b), _code(a), _stream()), "weighted_sum")
+    return out
 
 
 def transform_logits(logits: torch.Tensor, scale: float = 1.0, softcap: float = 0.0) -> torch.Tensor:
@@ -297,23 +359,158 @@ def qk_norm_rope_write(qkv: torch.Tensor, n_q: int, n_kv: int, head_dim: int, q_
 
 
 def attention_generic(q: torch.Tensor, cache, row_seq: torch.Tensor, row_pos: torch.Tensor, n_q: int, n_kv: int,
-                      head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+                      head_dim: int, scale: float, window: int = 0, gate: torch.Tensor | None = None,
+                      out_scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of every query row over its sequence's cached keys up to the
     row's own position (and not further back than ``window`` keys, if given).
-    ``q`` may be a column slice of a wider matrix (its row stride is passed on)."""
-    _need_cuda(q, cache.k, row_seq, row_pos)
+    ``q`` may be a column slice of a wider matrix (its row stride is passed on).  The values may
+    have a size of their own (the last dimension of ``cache.v``).  ``gate [rows, n_q]`` (a column
+    slice will do): head ``h`` of a row is multiplied by ``sigmoid(gate[row, h])``; ``out_scale``
+    multiplies everything; ``out``: where to write ``[rows, n_q * v_dim]`` (unit column stride)."""
+    _need_cuda(q, cache.k, row_seq, row_pos, gate)
     rows = q.shape[0]
-    assert q.stride(1) == 1 and q.shape[1] == n_q * head_dim
-    vec = 4 if q.dtype == torch.float32 else 8
-    if head_dim % vec or head_dim > 256:
-        raise KernelError(f"attention: head_dim {head_dim} must be a multiple of {vec} and at most 256")
+    v_dim = cache.v.shape[-1]
+    assert q.stride(1) == 1 and q.shape[1] == n_q * head_dim and cache.k.shape[-1] == head_dim
+    assert gate is None or (gate.dtype == q.dtype and gate.shape == (rows, n_q) and gate.stride(1) == 1)
+    if head_dim > 256 or v_dim > 256:
+        raise KernelError(f"attention: head_dim {head_dim} and the values' {v_dim} must be at most 256")
     if n_q % n_kv:
         raise KernelError(f"attention: {n_q} query heads are not a multiple of {n_kv} key/value heads")
-    out = torch.empty((rows, n_q * head_dim), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((rows, n_q * v_dim), dtype=q.dtype, device=q.device)
+    assert out.shape == (rows, n_q * v_dim) and out.stride(1) == 1 and out.dtype == q.dtype
     _check(_core().dfi_attention_generic(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
-        cache.block_table.shape[1], _ptr(row_seq), _ptr(row_pos), rows, n_q, n_kv, head_dim, cache.page_size,
-        cache.ring_tokens, window, _f(scale), _code(q), _stream()), "attention", f"head_dim {head_dim}")
+        cache.block_table.shape[1], _ptr(row_seq), _ptr(row_pos), rows, n_q, n_kv, head_dim, v_dim, cache.page_size,
+        cache.ring_tokens, window, _f(scale), _ptr(gate), gate.stride(0) if gate is not None else 0, _f(out_scale),
+        _code(q), _stream()), "attention", f"head_dim {head_dim}")
+    return out
+
+
+def head_norm_write(proj: torch.Tensor, n_q: int, n_kv: int, head_dim: int, v_dim: int, q_weight, k_weight,
+                    eps: float, row_pos: torch.Tensor, row_seq: torch.Tensor, cache) -> torch.Tensor:
+    """Per-head RMS norm (``x / sqrt(mean(x^2) + eps) * weight``, the weight shared by the heads; None: no
+    norm) of the query and key heads of ``proj [rows, n_q * head_dim + n_kv * head_dim + n_kv * v_dim + ...]``
+    without rotation: queries are rewritten in place, keys and values (whose size ``v_dim`` is their own) go to
+    ``cache`` at each row's position unless ``cache.writes`` is false.  Any sizes.  Returns the query view."""
+    _need_cuda(proj, row_pos, row_seq, cache.k, cache.v, cache.block_table)
+    rows, width = proj.shape
+    assert proj.stride(1) == 1 and width >= (n_q + n_kv) * head_dim + n_kv * v_dim
+    assert cache.k.dtype == proj.dtype and cache.k.is_contiguous() and cache.v.is_contiguous()
+    assert cache.k.shape[1:] == (n_kv, cache.page_size, head_dim) and cache.v.shape[1:] == (n_kv, cache.page_size, v_dim)
+    for w in (q_weight, k_weight):
+        assert w is None or (w.dtype == torch.float32 and w.numel() == head_dim)
+    _check(_core().dfi_head_norm_write(
+        _ptr(proj), rows, proj.stride(0), n_q, n_kv, head_dim, v_dim, _ptr(q_weight), _ptr(k_weight), _f(eps),
+        _ptr(row_pos), _ptr(row_seq), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table), cache.block_table.shape[1],
+        cache.page_size, cache.ring_tokens, 1 if cache.writes else 0, _code(proj), _stream()), "head_norm_write")
+    return proj[:, : n_q * head_dim]
+
+
+_SPLIT_SCRATCH: dict = {}
+
+
+def split_decode_parts(n_seqs: int, n_kv: int, longest: int) -> int:
+    """Into how many parts ``attention_split_decode`` cuts every sequence's keys: enough CTAs to fill the
+    device, at least 256 keys a part."""
+    sms = _core().dfi_sm_count()
+    return max(1, min(-(-2 * sms // max(1, n_seqs * n_kv)), -(-longest // 256), 64))
+
+
+def attention_split_decode(q: torch.Tensor, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float,
+                           window: int = 0, gate: torch.Tensor | None = None, out_scale: float = 1.0,
+                           out: torch.Tensor | None = None, n_parts: int | None = None) -> torch.Tensor:
+    """Attention for a step of one query row per sequence (row ``i`` is sequence ``i``), either dtype, any
+    head size up to 256 and values of a size of their own: every sequence's keys are cut into ``n_parts``
+    parts that run at once and are merged by a second kernel, which also applies ``sigmoid(gate)`` per
+    head and ``out_scale`` (see ``attention_generic``)."""
+    _need_cuda(q, cache.k, gate)
+    rows, v_dim = q.shape[0], cache.v.shape[-1]
+    assert rows == ctx.n_seqs and q.stride(1) == 1 and q.shape[1] == n_q * head_dim and cache.k.shape[-1] == head_dim
+    assert gate is None or (gate.dtype == q.dtype and gate.shape == (rows, n_q) and gate.stride(1) == 1)
+    if head_dim > 256 or v_dim > 256 or n_q % n_kv:
+        raise KernelError(f"attention_split_decode: head sizes {head_dim}/{v_dim} (at most 256), heads {n_q}/{n_kv}")
+    if n_parts is None:
+        n_parts = split_decode_parts(rows, n_kv, int(getattr(ctx, "max_kv_len", 0) or 1))
+    lib = _core()
+    lib.dfi_split_decode_floats.restype = ctypes.c_longlong
+    held = _scratch(_SPLIT_SCRATCH, q.device, lib.dfi_split_decode_floats(rows, n_q, v_dim, n_parts), 1)
+    if out is None:
+        out = torch.empty((rows, n_q * v_dim), dtype=q.dtype, device=q.device)
+    assert out.shape == (rows, n_q * v_dim) and out.stride(1) == 1 and out.dtype == q.dtype
+    global LAUNCHES
+    LAUNCHES += 1                                # the call launches two kernels
+    _check(lib.dfi_split_decode(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+        cache.block_table.shape[1], _ptr(ctx.seq_start), rows, n_q, n_kv, head_dim, v_dim, cache.page_size,
+        cache.ring_tokens, window, _f(scale), _ptr(gate), gate.stride(0) if gate is not None else 0, _f(out_scale),
+        n_parts, _ptr(held[0]), _code(q), _stream()), "attention_split_decode", f"head sizes {head_dim}/{v_dim}")
+    return out
+
+
+SCAN_DECAY_THEN_READ, SCAN_READ_THEN_DECAY = 0, 1
+
+
+def linear_scan(mode: int, q, k, v, gate, decay_logit: torch.Tensor, decay_bias, bonus, decay_param: float,
+                q_scale: float, state: torch.Tensor, ctx, n_heads: int, key_dim: int, value_dim: int, norm_weight,
+                norm_per_head: bool, eps: float, out: torch.Tensor, out_scale: float = 1.0, carry_rows=None,
+                carry_offset: int = 0) -> torch.Tensor:
+    """The recurrence of a matrix state ``S [key_dim, value_dim]`` per (sequence, head) over the step's rows,
+    in float32, in the order of the tokens (``csrc/linear_scan.cu``).
+
+    ``SCAN_DECAY_THEN_READ``: ``S = diag(a) S + k v^T; o = S^T q`` with ``a = sigmoid(z)^(1/decay_param)``;
+    ``SCAN_READ_THEN_DECAY``: ``o = (S + diag(bonus) k v^T)^T q; S = diag(a) S + k v^T`` with
+    ``a = exp(-exp(z))``; ``z = decay_logit + decay_bias`` (float32 ``[rows, heads * key_dim]`` and
+    ``[heads * key_dim]``).  ``q`` (times ``q_scale``), ``k``, ``v``, ``gate`` are ``[rows, heads * size]`` in
+    the engine's dtype and may be column slices.  Each head's ``o`` is divided by its root mean square over
+    ``value_dim`` (``eps`` inside the root), times ``norm_weight`` (``[value_dim]``, or ``[heads * value_dim]``
+    with ``norm_per_head``), times ``silu(gate)``, times ``out_scale``, and stored in ``out [rows, heads *
+    value_dim]``.  ``state [slots, floats]`` holds ``S`` of every head first; with ``carry_rows [rows, width]``
+    the last row of every sequence is also kept at ``carry_offset`` of its slot."""
+    _need_cuda(q, k, v, gate, decay_logit, decay_bias, bonus, state, out, carry_rows)
+    rows = q.shape[0]
+    for t, size in ((q, key_dim), (k, key_dim), (v, value_dim), (gate, value_dim), (out, value_dim)):
+        assert t.shape == (rows, n_heads * size) and t.stride(1) == 1 and t.dtype == out.dtype
+    assert decay_logit.dtype == torch.float32 and decay_logit.shape == (rows, n_heads * key_dim) and decay_logit.is_contiguous()
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+    assert state.shape[1] >= n_heads * key_dim * value_dim
+    for t in (decay_bias, bonus):
+        assert t is None or (t.dtype == torch.float32 and t.numel() == n_heads * key_dim and t.is_contiguous())
+    assert norm_weight is None or (norm_weight.dtype == torch.float32 and
+                                   norm_weight.numel() == (n_heads if norm_per_head else 1) * value_dim)
+    carry_width = 0
+    if carry_rows is not None:
+        assert carry_rows.dtype == out.dtype and carry_rows.is_contiguous() and carry_rows.shape[0] == rows
+        carry_width = carry_rows.shape[1]
+        assert carry_offset + carry_width <= state.shape[1]
+    if key_dim > 256 or value_dim > 256 or key_dim * value_dim > 128 * 256:
+        raise KernelError(f"linear_scan: a state of {key_dim} x {value_dim} per head is more than the kernel keeps "
+                          f"in registers (at most 256 x 128 or 128 x 256)")
+    _check(_core().dfi_linear_scan(
+        int(mode), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(gate), gate.stride(0),
+        _ptr(decay_logit), _ptr(decay_bias), _ptr(bonus), _f(decay_param), _f(q_scale), _ptr(state),
+        ctypes.c_longlong(state.stride(0)), _ptr(ctx.cu_rows), _ptr(ctx.seq_slot), ctx.n_seqs, n_heads, key_dim,
+        value_dim, _ptr(norm_weight), value_dim if norm_per_head else 0, _f(eps), _ptr(out), out.stride(0),
+        _f(out_scale), _ptr(carry_rows), carry_width, ctypes.c_longlong(carry_offset), _code(out), _stream()),
+        "linear_scan", f"state {key_dim} x {value_dim}")
+    return out
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, carry_offset: int, ctx) -> torch.Tensor:
+    """``out[s] = h + (before - h) * mu[s]`` for every blend ``s`` of ``mu [blends, width]`` (float32), where
+    ``before`` is the row above in the same sequence or, for a sequence's first row of the step, the row
+    kept at ``carry_offset`` of its slot in ``state`` (zeros when the sequence starts).  Returns
+    ``[blends, rows, width]`` in ``h``'s dtype."""
+    _need_cuda(h, mu, state)
+    rows, width = h.shape
+    assert h.is_contiguous() and mu.dtype == torch.float32 and mu.is_contiguous() and mu.shape[1] == width
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous()
+    assert carry_offset + width <= state.shape[1]
+    out = torch.empty((mu.shape[0], rows, width), dtype=h.dtype, device=h.device)
+    _check(_core().dfi_token_shift(_ptr(h), _ptr(mu), mu.shape[0], width, rows, _ptr(state),
+                                   ctypes.c_longlong(state.stride(0)), ctypes.c_longlong(carry_offset),
+                                   _ptr(ctx.row_seq), _ptr(ctx.cu_rows), _ptr(ctx.seq_slot), _ptr(out), _code(h),
+                                   _stream()), "token_shift")
     return out
 
 

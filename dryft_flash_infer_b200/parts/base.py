@@ -29,8 +29,11 @@ from .spec import PartSpec
 class TensorDecl:
     """One tensor a part wants from the model file.
 
-    It lands in rows ``row_start ...`` of the part's device buffer ``buffer``, so
-    that several file tensors can share one fused matrix without a second copy.
+    It lands in rows ``row_start ...`` (and, for a matrix, columns ``col_start ...``) of the
+    part's device buffer ``buffer``, so that several file tensors can share one fused matrix
+    without a second copy: stacked by rows when one product computes several results from the
+    same rows, side by side by columns when one product sums the results of several matrices.
+    A tensor without dimensions (a scalar) takes one element of a one-dimensional buffer.
     ``init`` picks the random-weights rule: ``matrix`` or ``norm``.  ``precision``
     is ``compute`` (held in the engine's dtype) or ``float32`` (always 32-bit).
     """
@@ -40,16 +43,23 @@ class TensorDecl:
     row_start: int = 0
     init: str = "matrix"
     precision: str = "compute"
+    col_start: int = 0
+
+    @property
+    def rows(self) -> int:
+        return self.shape[0] if self.shape else 1
 
 
 @dataclass(frozen=True)
 class KVNeed:
     """A mixer that keeps keys and values per token: heads, head size and, if not 0,
-    the window of latest tokens that it ever reads."""
+    the window of latest tokens that it ever reads.  ``v_head_dim``: the size of a value
+    where it differs from a key's (0: the same)."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
 
 
 @dataclass(frozen=True)
@@ -76,6 +86,13 @@ class Part:
     #: result to ``residual`` in place and returns the ``ScaledRows`` of the norm that follows
     fuses_add_norm = False
 
+    #: the engine's dtype (what matrices are held and rows are handed on in), told by the model
+    #: before the buffers are made
+    compute_dtype = None
+
+    def set_compute_dtype(self, dtype) -> None:
+        self.compute_dtype = dtype
+
     def tensors(self) -> dict[str, TensorDecl]:
         return {}
 
@@ -93,11 +110,21 @@ class Part:
     def buffer_shapes(self) -> dict[str, tuple[tuple[int, ...], str]]:
         out: dict[str, tuple[tuple[int, ...], str]] = {}
         for decl in self.tensors().values():
-            rows = decl.row_start + decl.shape[0]
-            shape, precision = out.get(decl.buffer, ((0,) + decl.shape[1:], decl.precision))
-            if shape[1:] != decl.shape[1:] or precision != decl.precision:
+            rows = decl.row_start + decl.rows
+            if len(decl.shape) == 2:
+                # matrices may also stand side by side: the buffer is as wide as the rightmost one reaches
+                shape, precision = out.get(decl.buffer, ((0, 0), decl.precision))
+                if len(shape) != 2 or precision != decl.precision:
+                    raise ValueError(f"tensors sharing buffer '{decl.buffer}' disagree on shape or precision")
+                out[decl.buffer] = ((max(shape[0], rows), max(shape[1], decl.col_start + decl.shape[1])), precision)
+                continue
+            if decl.col_start:
+                raise ValueError(f"only a matrix can start at a column of buffer '{decl.buffer}'")
+            tail = decl.shape[1:]
+            shape, precision = out.get(decl.buffer, ((0,) + tail, decl.precision))
+            if shape[1:] != tail or precision != decl.precision:
                 raise ValueError(f"tensors sharing buffer '{decl.buffer}' disagree on shape or precision")
-            out[decl.buffer] = ((max(shape[0], rows),) + decl.shape[1:], precision)
+            out[decl.buffer] = ((max(shape[0], rows),) + tail, precision)
         return out
 
 
@@ -155,7 +182,7 @@ class Block:
     #: the names of the norms this arrangement has; the layer's spec must give exactly these
     norm_names: tuple[str, ...] = ()
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: dict[str, Norm]):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, norms: dict[str, Norm]):
         if set(norms) != set(self.norm_names):
             raise ValueError(f"a '{self.kind}' block has the norms {sorted(self.norm_names)}, the layer gives "
                              f"{sorted(norms)}")
@@ -163,7 +190,10 @@ class Block:
         self.norms = dict(norms)
 
     def parts(self) -> dict[str, Part]:
-        return {"mixer": self.mixer, "feed_forward": self.feed_forward, **self.norms}
+        out = {"mixer": self.mixer, **self.norms}
+        if self.feed_forward is not None:
+            out["feed_forward"] = self.feed_forward
+        return out
 
     @property
     def first_norm(self) -> Norm | None:

@@ -16,6 +16,10 @@ class PreNormBlock(Block):
     the rows scaled by the norm's weight, and the product after it applies 1/rms.  Over a prompt's
     many bfloat16 rows the product takes the residual as its addend, so that the delta is never
     written, and the norm reads the sum alone.
+
+    A layer without a feed-forward (``feed_forward`` None) is the first half alone and has only
+    ``mixer_norm``.  The residual may be float32 while the parts work in the engine's dtype: the norms
+    then read float32 and add a delta of the engine's dtype into it (``Norm.add_forward``).
     """
 
     kind = "pre_norm"
@@ -23,8 +27,10 @@ class PreNormBlock(Block):
     fuses_next_norm = True
 
     def __init__(self, mixer, feed_forward, norms):
+        if feed_forward is None:
+            self.norm_names = ("mixer_norm",)
         super().__init__(mixer, feed_forward, norms)
-        self.mixer_norm, self.ffn_norm = self.norms["mixer_norm"], self.norms["ffn_norm"]
+        self.mixer_norm, self.ffn_norm = self.norms["mixer_norm"], self.norms.get("ffn_norm")
 
     @property
     def first_norm(self):
@@ -36,11 +42,22 @@ class PreNormBlock(Block):
 
     def forward(self, residual, pending, ctx, cache, state, next_norm=None):
         after = ctx.upcoming                     # what follows this block; the mixer is followed by the feed-forward
+        if self.feed_forward is None:
+            return self._mixer_only(residual, pending, ctx, cache, state)
         ctx.upcoming = self.feed_forward.first_weights()
         try:
             return self._forward(residual, pending, ctx, cache, state, next_norm, after)
         finally:
             ctx.upcoming = after
+
+    def _mixer_only(self, residual, pending, ctx, cache, state):
+        if isinstance(pending, kernels.ScaledRows):
+            normed = pending
+        elif pending is None:
+            normed = self.mixer_norm.forward(residual)
+        else:
+            normed = self.mixer_norm.add_forward(residual, pending)
+        return residual, self.mixer.forward(normed, ctx, cache, state)
 
     def _forward(self, residual, pending, ctx, cache, state, next_norm, after):
         fusable = kernels.add_norm_fusable(residual)

@@ -1,4 +1,4 @@
-"""The dense SwiGLU feed-forward."""
+"""Feed-forwards: the dense SwiGLU, and the plain two-matrix one with an element-wise activation."""
 
 from __future__ import annotations
 
@@ -44,3 +44,32 @@ class SwiGLU(FeedForward):
 
 
 register_part("feed_forward", SwiGLU.kind, SwiGLU)
+
+
+class DenseMLP(FeedForward):
+    """``down(act(up(x)))`` without biases or gate: ``activation`` is one of ``kernels.ACTIVATIONS``
+    (``relu2``: the square of relu)."""
+
+    kind = "dense_mlp"
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu2"):
+        if activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"a dense feed-forward knows the activations {sorted(kernels.ACTIVATIONS)}, got {activation!r}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.up = self.down = None
+
+    def tensors(self):
+        inter, hidden = self.intermediate_size, self.hidden_size
+        return {"up_proj": TensorDecl((inter, hidden), "up"), "down_proj": TensorDecl((hidden, inter), "down")}
+
+    def first_weights(self):
+        return kernels.next_weights(self.up)
+
+    def forward(self, x, ctx, add_norm=None):
+        inner = kernels.linear(x, self.up, then=kernels.next_weights(self.down))
+        kernels.activation(inner, self.activation)
+        return kernels.linear(inner, self.down, then=getattr(ctx, "upcoming", None))
+
+
+register_part("feed_forward", DenseMLP.kind, DenseMLP)

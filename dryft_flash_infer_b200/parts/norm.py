@@ -1,4 +1,4 @@
-"""RMSNorm, alone and with the residual add fused in front of it."""
+"""Norms: RMSNorm, alone and with the residual add fused in front of it, and Dynamic Tanh."""
 
 from __future__ import annotations
 
@@ -36,3 +36,31 @@ class RMSNorm(Norm):
 
 
 register_part("norm", RMSNorm.kind, RMSNorm)
+
+
+class DynamicTanh(Norm):
+    """``tanh(alpha * x) * weight + bias``, element by element: a norm that computes no mean and no
+    variance.  ``alpha`` is one learned number, ``weight`` and ``bias`` vectors; all three are held in
+    float32.  It reads a float32 residual stream (adding the delta of the layer before in float32
+    first, in the same pass) and hands on rows in the engine's dtype."""
+
+    kind = "dynamic_tanh"
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, dim: int | None = None):
+        self.dim = dim if dim is not None else hidden_size
+        self.weight = self.bias = self.alpha = None
+
+    def tensors(self):
+        return {"weight": TensorDecl((self.dim,), "weight", init="norm", precision="float32"),
+                "bias": TensorDecl((self.dim,), "bias", init="matrix", precision="float32"),
+                "alpha": TensorDecl((), "alpha", init="norm", precision="float32")}
+
+    def forward(self, x):
+        return kernels.dynamic_tanh(x, None, self.alpha, self.weight, self.bias, self.compute_dtype)
+
+    def add_forward(self, residual, delta):
+        return kernels.dynamic_tanh(residual, delta, self.alpha, self.weight, self.bias, self.compute_dtype)
+
+
+register_part("norm", DynamicTanh.kind, DynamicTanh)

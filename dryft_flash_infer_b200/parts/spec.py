@@ -32,7 +32,7 @@ class LayerSpec:
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None        # None: the layer has a mixer only (if its block kind allows that)
     norms: dict[str, PartSpec]
     tensor_names: dict[str, str]
 
@@ -72,6 +72,9 @@ class ModelSpec:
     embedding_scale: float = 1.0
     logit_scale: float = 1.0
     logit_softcap: float = 0.0
+    #: True: the residual stream is float32 whatever the engine's dtype (the embedding is widened, every
+    #: layer's delta is added in float32, norms read float32 and hand on the engine's dtype)
+    residual_float32: bool = False
     #: tensors that a model file may hold beside the expected ones without being an error
     ignorable_tensors: tuple[str, ...] = ()
 

@@ -241,11 +241,11 @@ def test_argmax_and_sampling():
 def test_sizes_a_kernel_does_not_take_are_refused():
     from dryft_flash_infer_b200.ops import KernelError, kernels
 
-    cache, _ = paged_cache(1, [10], 1, 20, torch.bfloat16)
-    q = torch.zeros(1, 20, dtype=torch.bfloat16).cuda()
+    cache, _ = paged_cache(1, [10], 1, 300, torch.bfloat16)
+    q = torch.zeros(1, 300, dtype=torch.bfloat16).cuda()
     pos = torch.zeros(1, dtype=torch.int32).cuda()
     with pytest.raises(KernelError, match="head_dim"):
-        kernels.attention_generic(q, cache, pos, pos, 1, 1, 20, 1.0)
+        kernels.attention_generic(q, cache, pos, pos, 1, 1, 300, 1.0)
     with pytest.raises(KernelError, match="CUDA device"):
         kernels.rms_norm(torch.zeros(2, 8), torch.ones(8), 1e-6)
     with pytest.raises(KernelError, match="dtype"):
