@@ -144,7 +144,7 @@ def random_tensors(config, seed, dtype=torch.bfloat16):
     width, vocab = config["width"], config["vocab"]
 
     def normal(*shape, std=1.0, mean=0.0):
-        return (torch.randn(*shape, generator=g) * std + mean).to(dtype)
+        return (torch.randn(tuple(shape), generator=g) * std + mean).to(dtype)
 
     def matrix(out, inner, gain=1.0):
         return normal(out, inner, std=gain / math.sqrt(inner))
