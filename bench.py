@@ -256,6 +256,185 @@ def generation_run(shape: str) -> int:
     return 0
 
 
+# ---- the Sasilorn architecture beside Qwen3 at equal width, depth and weights per layer (--arch sasilorn)
+def sasilorn_config(width: int, layers: int, vocab: int) -> dict:
+    """Layers in turn: time mixing (heads of 64) and attention beside linear attention, each with a squared-relu
+    feed-forward sized so that a layer holds about what a Qwen3 layer of this width holds (39.5 width^2 / 2.5)."""
+    heads = width // 128
+    per_layer = qwen_like(width, 1, vocab)
+    budget = (per_layer["num_attention_heads"] + 2 * per_layer["num_key_value_heads"]) * 128 * width \
+        + width * per_layer["num_attention_heads"] * 128 + 3 * per_layer["intermediate_size"] * width
+    wkv = {"type": "wkv", "mixer": {"heads": width // 64, "dim": 64, "rank": 64}}
+    wkv["mlp"] = {"kind": "dense", "ff": (budget - 5 * width * width) // (2 * width) // 64 * 64}
+    left = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+    right = {"heads": heads // 2, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 64}
+    mixer_weights = width * ((left["heads"] + left["kv_heads"]) * 128 + left["kv_heads"] * 128 + left["heads"] * 128) \
+        + width * right["heads"] * (2 * 64 + 3 * 128)
+    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 0.9},
+           "mlp": {"kind": "dense", "ff": (budget - mixer_weights) // (2 * width) // 64 * 64}}
+    return {"architecture": "Sasilorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [wkv if i % 2 == 0 else par for i in range(layers)]}
+
+
+def qwen_like(width: int, layers: int, vocab: int) -> dict:
+    heads = width // 128
+    return dict(QWEN3_4B, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads * 32 // 20 // 4 * 4 or 4,
+                num_key_value_heads=max(1, (heads * 32 // 20 // 4 * 4 or 4) // 4), intermediate_size=width * 38 // 10 // 64 * 64,
+                vocab_size=vocab, tie_word_embeddings=False)
+
+
+def timed(fn, repeats: int = 5, flush=None):
+    """Median device time of ``fn()`` in microseconds, by CUDA events, after two untimed calls; ``flush`` (a
+    buffer larger than L2) is rewritten before every timed call."""
+    import torch
+
+    times = []
+    for i in range(2 + repeats):
+        if flush is not None:
+            flush.add_(1)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(a.elapsed_time(b) * 1e3)
+    return statistics.median(times)
+
+
+def sasilorn_kernels(width: int, tokens: int, batch: int, context: int, peak: dict) -> dict:
+    """The hot kernels of the new design by themselves, beside the like kernels of Qwen3, each with its roofline
+    fraction: attention over a prompt (tensor cores), attention for one token a sequence (cache bytes), the
+    state recurrence over a prompt (float32 pipes) and for one token (state bytes), and the norms (row bytes)."""
+    import numpy as np
+    import torch
+    from types import SimpleNamespace
+    from dryft_flash_infer_b200.cache.storage import LayerCache
+    from dryft_flash_infer_b200.ops import kernels
+
+    dev, bf = "cuda", torch.bfloat16
+    flush = torch.zeros(160 << 20, dtype=torch.float32, device=dev)             # 640 MB: L2 holds 126 MB
+    heads, kv, d = width // 128, max(1, width // 512), 128
+    out = {}
+    tflops = lambda flops, us: flops / (us * 1e-6) / 1e12
+    gbs = lambda nbytes, us: nbytes / (us * 1e-6) / 1e9
+
+    def paged(n_seqs, length, dk, dv):
+        pages = -(-length // 64)
+        table = (1 + torch.arange(n_seqs * pages, dtype=torch.int32).view(n_seqs, pages)).to(dev)
+        k = torch.randn(1 + n_seqs * pages, kv, 64, dk, device=dev).to(bf)
+        v = torch.randn(1 + n_seqs * pages, kv, 64, dv, device=dev).to(bf)
+        return LayerCache(k, v, table, 64, 0, True)
+
+    # attention over a prompt of `tokens`: ours (keys 128, values 128) and Qwen3's tcgen05 kernel (128)
+    cache = paged(1, tokens, d, d)
+    q = torch.randn(tokens, heads * d, device=dev).to(bf)
+    gate = torch.randn(tokens, heads, device=dev).to(bf)
+    ctx = SimpleNamespace(n_seqs=1, max_q_len=tokens, seq_start=torch.zeros(1, dtype=torch.int32, device=dev),
+                          cu_rows=torch.tensor([0, tokens], dtype=torch.int32, device=dev))
+    flops = 4.0 * heads * d * tokens * tokens / 2
+    us = timed(lambda: kernels.attention_split_prefill(q, cache, ctx, heads, kv, d, d ** -0.5, gate=gate), flush=flush)
+    out["attention_prompt"] = {"us": round(us, 1), "tflops": round(tflops(flops, us), 1),
+                               "frac": round(tflops(flops, us) / peak["bf16_tflops"], 4), "kernel": "attention_split_prefill (mma.sync)"}
+    us = timed(lambda: kernels.attention_prefill_tc(q, cache, ctx, heads, kv, d, d ** -0.5), flush=flush)
+    out["attention_prompt_qwen3"] = {"us": round(us, 1), "tflops": round(tflops(flops, us), 1),
+                                     "frac": round(tflops(flops, us) / peak["bf16_tflops"], 4), "kernel": "attention_prefill_tc (tcgen05)"}
+    us = timed(lambda: kernels.attention_prefill(q, cache, ctx, heads, kv, d, d ** -0.5), flush=flush)
+    out["attention_prompt_qwen3_other_head_sizes"] = {"us": round(us, 1), "tflops": round(tflops(flops, us), 1),
+                                                      "frac": round(tflops(flops, us) / peak["bf16_tflops"], 4), "kernel": "attention_prefill (mma.sync)"}
+    # attention for one token of `batch` sequences at `context`
+    cache = paged(batch, context, d, d)
+    q1 = torch.randn(batch, heads * d, device=dev).to(bf)
+    g1 = torch.randn(batch, heads, device=dev).to(bf)
+    dctx = SimpleNamespace(n_seqs=batch, max_kv_len=context, decode_plans=None,
+                           seq_start=torch.full((batch,), context - 1, dtype=torch.int32, device=dev))
+    nbytes = batch * context * kv * 2 * d * 2
+    us = timed(lambda: kernels.attention_split_decode(q1, cache, dctx, heads, kv, d, d ** -0.5, gate=g1), flush=flush)
+    out["attention_token"] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
+                              "kernel": "split_decode + merge"}
+    us = timed(lambda: kernels.attention_decode(q1, cache, dctx, heads, kv, d, d ** -0.5), flush=flush)
+    out["attention_token_qwen3"] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
+                                    "kernel": "attention_decode (mma.sync, stream-K)"}
+    # the state recurrence: time mixing with heads of 64 x 64
+    H, D, V = width // 64, 64, 64
+    for name, rows, n_seqs in (("scan_prompt", tokens, 1), ("scan_token", batch, batch)):
+        r, k, v, g = (torch.randn(rows, H * D, device=dev).to(bf) for _ in range(4))
+        z = torch.randn(rows, H * D, device=dev) - 1.0
+        w0, u, norm = torch.zeros(H * D, device=dev), torch.randn(H * D, device=dev), torch.ones(H * V, device=dev)
+        state = torch.zeros(n_seqs, H * D * V, device=dev)
+        res = torch.empty(rows, H * V, device=dev, dtype=bf)
+        per = rows // n_seqs
+        sctx = SimpleNamespace(n_seqs=n_seqs, cu_rows=torch.arange(0, rows + 1, per, dtype=torch.int32, device=dev),
+                               seq_slot=torch.arange(n_seqs, dtype=torch.int32, device=dev))
+        us = timed(lambda: kernels.linear_scan(kernels.SCAN_READ_THEN_DECAY, r, k, v, g, z, w0, u, 0.0, 1.0, state, sctx, H, D, V,
+                                               norm, True, 1e-5, res), flush=flush)
+        if n_seqs == 1:
+            flops = 7.0 * rows * H * D * V
+            out[name] = {"us": round(us, 1), "fp32_tflops": round(tflops(flops, us), 2), "tokens": rows,
+                         "us_per_token": round(us / rows, 4), "kernel": "linear_scan (float32 pipes, in the order of the tokens)"}
+        else:
+            nbytes = 2 * n_seqs * H * D * V * 4
+            out[name] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
+                         "kernel": "linear_scan"}
+    # the norms over a prompt's rows
+    x32, delta = torch.randn(tokens, width, device=dev), torch.randn(tokens, width, device=dev).to(bf)
+    one, w, b = torch.ones(1, device=dev), torch.ones(width, device=dev), torch.zeros(width, device=dev)
+    us = timed(lambda: kernels.dynamic_tanh(x32, delta, one, w, b, bf), flush=flush)
+    nbytes = tokens * width * (4 + 4 + 2 + 2)
+    out["norm_prompt"] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
+                          "kernel": "dynamic_tanh with the float32 residual add"}
+    x16 = torch.randn(tokens, width, device=dev).to(bf)
+    us = timed(lambda: kernels.add_rms_norm(x16, delta, w, 1e-6), flush=flush)
+    nbytes = tokens * width * (2 + 2 + 2 + 2)
+    out["norm_prompt_qwen3"] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
+                                "kernel": "rmsnorm with the bfloat16 residual add"}
+    return out
+
+
+def sasilorn_run(steps: int, warmup: int, widths=(1024, 2560), layers: int = 8, vocab: int = 32768) -> int:
+    """Prefill and decode throughput of Sasilorn beside Qwen3 at equal width, depth and weights per layer
+    (random weights), and the design's hot kernels beside the like kernels of Qwen3 with their roofline fractions."""
+    import torch
+    from dryft_flash_infer_b200 import Engine, StepEntry
+
+    peak = peaks()
+    batch, context, tokens = BATCH, 2048, PREFILL_TOKENS
+    steps = min(steps, 64)
+    sizes = []
+    for width in widths:
+        row = {"width": width, "layers": layers}
+        for arch, cfg in (("sasilorn", sasilorn_config(width, layers, vocab)), ("qwen3", qwen_like(width, layers, vocab))):
+            engine = Engine(config=cfg, random_weights=True, seed=0, dtype="bfloat16", max_tokens=(batch + 1) * context,
+                            max_seqs=batch + 1, max_context=context)
+            for group in engine.cache.groups:
+                group.k.normal_(0.0, 1.0)
+                group.v.normal_(0.0, 1.0)
+            g = torch.Generator().manual_seed(0)
+            prompt = torch.randint(0, vocab, (tokens,), generator=g).tolist()
+
+            def prefill():
+                slot = engine.open_slot()
+                engine.step([StepEntry(slot, prompt, [tokens - 1])])
+                engine.close_slot(slot)
+
+            ms = timed(prefill, repeats=3) / 1e3
+            decode_ms, launches = time_decode(engine, batch, context, steps, warmup)
+            row[arch] = {"weights_mb": round(engine.model.weight_bytes() / 2 ** 20), "prefill_ms": round(ms, 3),
+                         "prefill_tokens_per_s": round(tokens / ms * 1e3), "decode_ms_per_step": round(decode_ms, 4),
+                         "decode_tokens_per_s": round(batch / decode_ms * 1e3), "launches_per_decode_step": launches,
+                         "decode_weight_stream_frac": round(engine.model.weight_bytes() / (decode_ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)}
+            del engine
+            torch.cuda.empty_cache()
+        sizes.append(row)
+    line = {"arch": "sasilorn", "beside": "qwen3", "dtype": "bf16", "data": "synthetic: random weights, random token ids",
+            "prefill_tokens": tokens, "decode_batch": batch, "decode_context": context, "steps": steps, "warmup": warmup,
+            "peaks": peak, "sizes": sizes, "kernels": sasilorn_kernels(widths[-1], tokens, batch, context, peak)}
+    print(json.dumps(line))
+    return 0
+
+
+
 def headline_config(layers: int) -> dict:
     cfg = QWEN3_4B
     return {"model": "Qwen3-4B sizes", "layers": layers, "layers_of_config": cfg["num_hidden_layers"],
@@ -356,6 +535,9 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=CONTEXT, help="context length of the --profile decode steps")
     parser.add_argument("--shape", choices=["4b", "8b", "14b"], default="4b",
                         help="8b / 14b: the end-to-end generation runs of the larger shapes instead of the headline run")
+    parser.add_argument("--arch", choices=["qwen3", "sasilorn"], default="qwen3",
+                        help="sasilorn: prefill and decode of the Sasilorn architecture beside Qwen3 at equal sizes, and its "
+                             "hot kernels with roofline fractions, instead of the headline run (one JSON line of its own)")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run it with --gpus 1")
@@ -364,6 +546,8 @@ def main() -> int:
     steps = max(1, args.steps)
     if args.impl == "reference":
         return reference_run(steps, warmup, args.quick)
+    if args.arch == "sasilorn":
+        return sasilorn_run(steps, warmup)
     if args.shape != "4b":
         return generation_run(args.shape)
 

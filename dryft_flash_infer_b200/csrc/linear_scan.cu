@@ -10,12 +10,14 @@
 // reads are float32 whatever the storage type of q, k, v; the recurrence runs in the order of the tokens,
 // so a prompt taken whole, in portions or token by token gives the same state up to nothing at all.
 //
-// One CTA of eight warps owns one (sequence, head) for all the tokens the step brings it.  Warp w keeps
-// rows [w NI, (w+1) NI) of S in registers, lane c the columns c, c + 32, ...; tokens are taken sixteen at
-// a time: their q, k, decays and v are staged in shared memory as float32 (the decay computed once per
-// token and channel), every warp leaves its share of o_t there, and after the sixteen tokens the warps
-// sum the shares token by token, divide a head's output by its root mean square, weight it, gate it with
-// silu(g) and store it: the norm and the gate cost no pass of their own.
+// One CTA of eight warps owns one (sequence, head, 32 columns of S) for all the tokens the step brings
+// it: a column of S needs no other column, so a head spreads over V / 32 CTAs.  Warp w keeps rows
+// [w NI, (w+1) NI) of its columns in registers, lane c column c.  Tokens are taken sixteen at a time: their
+// q, k, decays and v wait in shared memory as float32 (the decay computed once per token and channel);
+// while the sixteen are worked through, the next sixteen are already on their way from global memory into
+// registers.  Every warp leaves its rows' share of o_t in shared memory; after the sixteen tokens the
+// shares are summed and stored as float32.  A second kernel, one warp per (row, head), divides a head's
+// output by its root mean square, weights it, gates it with silu(g) and stores it in the storage type.
 //
 // The token shift of the time-mixing layer (every projection reads its own blend of a token's row and
 // the row before it) is the other kernel here; the row that a sequence's next step will need lives in
@@ -25,7 +27,7 @@
 namespace dfi {
 
 constexpr int kScanWarps = 8;
-constexpr int kScanTokens = 16;
+constexpr int kScanTokens = 16;     // tokens staged in shared memory at a time
 
 struct ScanArgs {
     const void* q; const void* k; const void* v; const void* g;       // [rows, *_stride] in the storage type
@@ -40,19 +42,21 @@ struct ScanArgs {
     const int* cu_rows;            // [sequences + 1]
     const int* seq_slot;           // [sequences]
     int H, D, V;
-    const float* norm_weight;      // [V] (norm_head_stride 0) or [H, V] (norm_head_stride V); null: no weight
-    int norm_head_stride;
-    float eps;
-    void* out; int out_stride;     // [rows, out_stride]: H heads of V
-    float out_scale;
+    float* raw;                    // [rows, H * V]: the reads o_t before norm and gate
     const void* carry_rows;        // or null: [rows, carry_width] rows whose last one per sequence is kept in the state
     int carry_width;
     long long carry_offset;        // where in a slot that row lives
     int bf16;                      // storage type of q, k, v, g, out, carry_rows
 };
 
+// Through the read-only path (ld.global.nc): the rows are written by earlier kernels only, and a load that
+// cannot alias shared memory may be issued ahead of the stores into it.
 __device__ __forceinline__ float load_as_float(const void* p, size_t i, int is_bf16) {
-    return is_bf16 ? __bfloat162float(reinterpret_cast<const bf16*>(p)[i]) : reinterpret_cast<const float*>(p)[i];
+    if (is_bf16) {
+        const unsigned short raw = __ldg(reinterpret_cast<const unsigned short*>(p) + i);
+        return __uint_as_float((unsigned int)raw << 16);
+    }
+    return __ldg(reinterpret_cast<const float*>(p) + i);
 }
 __device__ __forceinline__ void store_from_float(void* p, size_t i, float v, int is_bf16) {
     if (is_bf16) reinterpret_cast<bf16*>(p)[i] = __float2bfloat16_rn(v);
@@ -69,63 +73,90 @@ __device__ __forceinline__ float decay_of(float z, float param) {
     return expf(-expf(z));
 }
 
-template <int MODE, int NI, int NC>
+// What a thread fetches for the chunk of up to TC tokens at row c0: elements tid, tid + THREADS, ... of
+// [TC][DP] (q, k, decay logits) and of [TC][32] (v); zeros past the chunk's tokens and the head's sizes.
+template <int TC, int DP, int PER, int PER_V>
+__device__ __forceinline__ void scan_fetch(const ScanArgs& a, int c0, int row1, int head, int j, int tid,
+                                           float (&fq)[PER], float (&fk)[PER], float (&fz)[PER], float (&fv)[PER_V]) {
+    constexpr int THREADS = kScanWarps * 32;
+    const int nt = min(TC, row1 - c0), D = a.D, V = a.V, HD = a.H * a.D;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int idx = tid + e * THREADS, t = idx / DP, i = idx - t * DP;
+        fq[e] = 0.f; fk[e] = 0.f; fz[e] = 0.f;
+        if (t < nt && i < D) {
+            const size_t row = (size_t)(c0 + t);
+            const int col = head * D + i;
+            fq[e] = load_as_float(a.q, row * a.q_stride + col, a.bf16);
+            fk[e] = load_as_float(a.k, row * a.k_stride + col, a.bf16);
+            fz[e] = __ldg(a.decay_logit + row * HD + col);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < PER_V; ++e) {
+        const int idx = tid + e * THREADS, t = idx >> 5;
+        fv[e] = (t < nt && j < V) ? load_as_float(a.v, (size_t)(c0 + t) * a.v_stride + head * V + j, a.bf16) : 0.f;
+    }
+}
+
+template <int MODE, int NI>
 __global__ void __launch_bounds__(kScanWarps * 32) linear_scan_kernel(const ScanArgs a) {
-    extern __shared__ __align__(16) float smem[];
-    constexpr int DP = kScanWarps * NI, VP = 32 * NC, TC = kScanTokens;
-    float* rs = smem;                    // [TC][DP]
-    float* ks = rs + TC * DP;            // [TC][DP]
-    float* ws = ks + TC * DP;            // [TC][DP]
-    float* vs = ws + TC * DP;            // [TC][VP]
-    float* op = vs + TC * VP;            // [TC][warps][VP]
+    constexpr int TC = NI >= 32 ? kScanTokens / 2 : kScanTokens;      // the widest heads take eight tokens at a time
+    constexpr int DP = kScanWarps * NI, THREADS = kScanWarps * 32;
+    constexpr int PER = TC * DP / THREADS;            // elements of q, k, z a thread fetches per chunk
+    constexpr int PER_V = TC * 32 / THREADS;          // and of v
+    __shared__ __align__(16) float rs[TC * DP];
+    __shared__ __align__(16) float ks[TC * DP];
+    __shared__ __align__(16) float ws[TC * DP];
+    __shared__ float vs[TC * 32];
+    __shared__ float op[TC * kScanWarps * 32];
     pdl_launch_next();
     pdl_wait();
     const int seq = blockIdx.x, head = blockIdx.y;
     const int row0 = a.cu_rows[seq], row1 = a.cu_rows[seq + 1];
     if (row1 <= row0) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int D = a.D, V = a.V, HD = a.H * a.D;
+    const int D = a.D, V = a.V;
+    const int j = blockIdx.z * 32 + lane;             // this lane's column of S
     float* S_g = a.state + (size_t)a.seq_slot[seq] * a.slot_stride + (size_t)head * D * V;
     const int i0 = warp * NI;
 
-    float S[NC][NI], U[NI];
+    float S[NI], U[NI];
 #pragma unroll
     for (int n = 0; n < NI; ++n) {
         const int i = i0 + n;
         U[n] = (MODE == 1 && i < D) ? a.bonus[head * D + i] : 0.f;
-#pragma unroll
-        for (int m = 0; m < NC; ++m) {
-            const int j = lane + 32 * m;
-            S[m][n] = (i < D && j < V) ? S_g[(size_t)i * V + j] : 0.f;
-        }
+        S[n] = (i < D && j < V) ? S_g[(size_t)i * V + j] : 0.f;
     }
 
+    float fq[PER], fk[PER], fz[PER], fv[PER_V];
+    float bias[PER];
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+        const int i = (tid + e * THREADS) % DP;
+        bias[e] = (a.decay_bias != nullptr && i < D) ? a.decay_bias[head * D + i] : 0.f;
+    }
+
+    scan_fetch<TC, DP, PER, PER_V>(a, row0, row1, head, j, tid, fq, fk, fz, fv);
     for (int c0 = row0; c0 < row1; c0 += TC) {
         const int nt = min(TC, row1 - c0);
-        __syncthreads();
-        for (int idx = tid; idx < nt * DP; idx += kScanWarps * 32) {
-            const int t = idx / DP, i = idx - t * DP;
-            const size_t row = (size_t)(c0 + t);
-            float r = 0.f, k = 0.f, w = 1.f;
-            if (i < D) {
-                const int col = head * D + i;
-                r = load_as_float(a.q, row * a.q_stride + col, a.bf16) * a.q_scale;
-                k = load_as_float(a.k, row * a.k_stride + col, a.bf16);
-                float z = a.decay_logit[row * HD + col];
-                if (a.decay_bias != nullptr) z += a.decay_bias[col];
-                w = decay_of<MODE>(z, a.decay_param);
-            }
-            rs[idx] = r; ks[idx] = k; ws[idx] = w;
-        }
-        for (int idx = tid; idx < nt * VP; idx += kScanWarps * 32) {
-            const int t = idx / VP, j = idx - t * VP;
-            vs[idx] = j < V ? load_as_float(a.v, (size_t)(c0 + t) * a.v_stride + head * V + j, a.bf16) : 0.f;
-        }
-        __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            float o[NC], vj[NC];
+        __syncthreads();                               // the chunk before is done with shared memory
 #pragma unroll
-            for (int m = 0; m < NC; ++m) { o[m] = 0.f; vj[m] = vs[t * VP + lane + 32 * m]; }
+        for (int e = 0; e < PER; ++e) {
+            const int idx = tid + e * THREADS, i = idx % DP;
+            rs[idx] = fq[e] * a.q_scale;
+            ks[idx] = fk[e];
+            ws[idx] = i < D ? decay_of<MODE>(fz[e] + bias[e], a.decay_param) : 1.f;
+        }
+#pragma unroll
+        for (int e = 0; e < PER_V; ++e) vs[tid + e * THREADS] = fv[e];
+        __syncthreads();
+        if (c0 + TC < row1)                            // on its way while this chunk is worked through
+            scan_fetch<TC, DP, PER, PER_V>(a, c0 + TC, row1, head, j, tid, fq, fk, fz, fv);
+#pragma unroll 2
+        for (int t = 0; t < nt; ++t) {
+            const float vj = vs[t * 32 + lane];
+            float o = 0.f;
             const float4* r4 = reinterpret_cast<const float4*>(rs + t * DP + i0);
             const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP + i0);
             const float4* w4 = reinterpret_cast<const float4*>(ws + t * DP + i0);
@@ -136,105 +167,82 @@ __global__ void __launch_bounds__(kScanWarps * 32) linear_scan_kernel(const Scan
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int n = n4 * 4 + e;
-#pragma unroll
-                    for (int m = 0; m < NC; ++m) {
-                        if (MODE == 0) {
-                            S[m][n] = fmaf(w[e], S[m][n], k[e] * vj[m]);
-                            o[m] = fmaf(r[e], S[m][n], o[m]);
-                        } else {
-                            const float kv = k[e] * vj[m];
-                            o[m] = fmaf(r[e], fmaf(U[n], kv, S[m][n]), o[m]);
-                            S[m][n] = fmaf(w[e], S[m][n], kv);
-                        }
+                    if (MODE == 0) {
+                        S[n] = fmaf(w[e], S[n], k[e] * vj);
+                        o = fmaf(r[e], S[n], o);
+                    } else {
+                        const float kv = k[e] * vj;
+                        o = fmaf(r[e], fmaf(U[n], kv, S[n]), o);
+                        S[n] = fmaf(w[e], S[n], kv);
                     }
                 }
             }
-#pragma unroll
-            for (int m = 0; m < NC; ++m) op[(t * kScanWarps + warp) * VP + lane + 32 * m] = o[m];
+            op[(t * kScanWarps + warp) * 32 + lane] = o;
         }
         __syncthreads();
-        // the sixteen tokens' outputs: sum the warps' shares, unit root mean square over V, weight, gate
+        // the chunk's reads: the warps' shares summed, float32, a row's 32 columns side by side
         for (int t = warp; t < nt; t += kScanWarps) {
-            const size_t row = (size_t)(c0 + t);
-            float o[NC], ssq = 0.f;
+            float sum = 0.f;
 #pragma unroll
-            for (int m = 0; m < NC; ++m) {
-                float sum = 0.f;
-#pragma unroll
-                for (int w8 = 0; w8 < kScanWarps; ++w8) sum += op[(t * kScanWarps + w8) * VP + lane + 32 * m];
-                o[m] = sum;
-                ssq += sum * sum;           // columns from V on are zero
-            }
-            ssq = warp_sum(ssq);
-            const float factor = a.out_scale / sqrtf(ssq / (float)V + a.eps);
-#pragma unroll
-            for (int m = 0; m < NC; ++m) {
-                const int j = lane + 32 * m;
-                if (j < V) {
-                    float val = o[m] * factor;
-                    if (a.norm_weight != nullptr) val *= a.norm_weight[head * a.norm_head_stride + j];
-                    if (a.g != nullptr) {
-                        const float gate = load_as_float(a.g, row * a.g_stride + head * V + j, a.bf16);
-                        val *= gate / (1.f + expf(-gate));
-                    }
-                    store_from_float(a.out, row * a.out_stride + head * V + j, val, a.bf16);
-                }
-            }
+            for (int w8 = 0; w8 < kScanWarps; ++w8) sum += op[(t * kScanWarps + w8) * 32 + lane];
+            if (j < V) a.raw[(size_t)(c0 + t) * (a.H * V) + head * V + j] = sum;
         }
     }
 #pragma unroll
     for (int n = 0; n < NI; ++n) {
         const int i = i0 + n;
-#pragma unroll
-        for (int m = 0; m < NC; ++m) {
-            const int j = lane + 32 * m;
-            if (i < D && j < V) S_g[(size_t)i * V + j] = S[m][n];
-        }
+        if (i < D && j < V) S_g[(size_t)i * V + j] = S[n];
     }
-    if (a.carry_rows != nullptr && head == 0) {
+    if (a.carry_rows != nullptr && head == 0 && blockIdx.z == 0) {
         float* dst = a.state + (size_t)a.seq_slot[seq] * a.slot_stride + a.carry_offset;
-        for (int c = tid; c < a.carry_width; c += kScanWarps * 32)
+        for (int c = tid; c < a.carry_width; c += THREADS)
             dst[c] = load_as_float(a.carry_rows, (size_t)(row1 - 1) * a.carry_width + c, a.bf16);
     }
 }
 
-template <int MODE, int NI, int NC>
-static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t st) {
-    constexpr int DP = kScanWarps * NI, VP = 32 * NC;
-    const size_t bytes = sizeof(float) * kScanTokens * (3 * DP + VP + kScanWarps * VP);
-    if (bytes > 48 * 1024) {
-        static bool raised = false;          // per instantiation
-        if (!raised) {
-            if (cudaFuncSetAttribute(linear_scan_kernel<MODE, NI, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)bytes) != cudaSuccess) {
-                cudaGetLastError();
-                return DFI_ERR_LAUNCH;
-            }
-            raised = true;
+// out[row, head] = raw[row, head] / rms(raw[row, head]) * weight * silu(g[row, head]) * out_scale: one warp per
+// (row, head); weight [V] (norm_head_stride 0) or [H, V] (norm_head_stride V) or null; g null: no gate.
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ raw, int H, int V, const float* __restrict__ weight,
+                                      int norm_head_stride, float eps, const T* __restrict__ g, int g_stride,
+                                      float out_scale, T* __restrict__ out, int out_stride) {
+    pdl_launch_next();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (head >= H) return;
+    const size_t row = blockIdx.x;
+    const float* src = raw + row * ((size_t)H * V) + (size_t)head * V;
+    float ssq = 0.f;
+    for (int c = lane; c < V; c += 32) ssq += src[c] * src[c];
+    ssq = warp_sum(ssq);
+    const float factor = out_scale / sqrtf(ssq / (float)V + eps);
+    for (int c = lane; c < V; c += 32) {
+        float val = src[c] * factor;
+        if (weight != nullptr) val *= weight[head * norm_head_stride + c];
+        if (g != nullptr) {
+            const float gate = to_float(g[row * g_stride + head * V + c]);
+            val *= gate / (1.f + expf(-gate));
         }
+        out[row * out_stride + head * V + c] = from_float<T>(val);
     }
-    launch(linear_scan_kernel<MODE, NI, NC>, dim3(n_seqs, a.H), dim3(kScanWarps * 32), bytes, st, a);
+}
+
+template <int MODE, int NI>
+static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t st) {
+    const int slices = (a.V + 31) / 32;
+    if (slices > 65535) return DFI_ERR_LIMIT;
+    launch(linear_scan_kernel<MODE, NI>, dim3(n_seqs, a.H, slices), dim3(kScanWarps * 32), 0, st, a);
     DFI_CHECK_LAUNCH();
     return DFI_OK;
 }
 
-template <int MODE, int NI>
-static int pick_columns(const ScanArgs& a, int n_seqs, cudaStream_t st) {
-    if (a.V <= 32) return launch_scan<MODE, NI, 1>(a, n_seqs, st);
-    if (a.V <= 64) return launch_scan<MODE, NI, 2>(a, n_seqs, st);
-    if (a.V <= 128) return launch_scan<MODE, NI, 4>(a, n_seqs, st);
-    if constexpr (NI <= 16) {
-        if (a.V <= 256) return launch_scan<MODE, NI, 8>(a, n_seqs, st);
-    }
-    return DFI_ERR_LIMIT;
-}
-
 template <int MODE>
 static int pick_rows(const ScanArgs& a, int n_seqs, cudaStream_t st) {
-    if (a.D <= 32) return pick_columns<MODE, 4>(a, n_seqs, st);
-    if (a.D <= 64) return pick_columns<MODE, 8>(a, n_seqs, st);
-    if (a.D <= 128) return pick_columns<MODE, 16>(a, n_seqs, st);
-    if (a.D <= 256) return pick_columns<MODE, 32>(a, n_seqs, st);
+    if (a.D <= 32) return launch_scan<MODE, 4>(a, n_seqs, st);
+    if (a.D <= 64) return launch_scan<MODE, 8>(a, n_seqs, st);
+    if (a.D <= 128) return launch_scan<MODE, 16>(a, n_seqs, st);
+    if (a.D <= 256) return launch_scan<MODE, 32>(a, n_seqs, st);
     return DFI_ERR_LIMIT;
 }
 
@@ -273,11 +281,13 @@ DFI_EXPORT int dfi_linear_scan(int mode, const void* q, int q_stride, const void
                                int v_stride, const void* g, int g_stride, const float* decay_logit,
                                const float* decay_bias, const float* bonus, float decay_param, float q_scale,
                                float* state, long long slot_stride, const int* cu_rows, const int* seq_slot,
-                               int n_seqs, int H, int D, int V, const float* norm_weight, int norm_head_stride,
-                               float eps, void* out, int out_stride, float out_scale, const void* carry_rows,
-                               int carry_width, long long carry_offset, int dtype, void* stream) {
+                               int n_seqs, int rows, int H, int D, int V, const float* norm_weight,
+                               int norm_head_stride, float eps, float* raw, void* out, int out_stride,
+                               float out_scale, const void* carry_rows, int carry_width, long long carry_offset,
+                               int dtype, void* stream) {
     if (n_seqs <= 0) return DFI_OK;
-    if (H <= 0 || H > 65535 || D <= 0 || V <= 0 || state == nullptr || decay_logit == nullptr) return DFI_ERR_SHAPE;
+    if (H <= 0 || H > 65535 || D <= 0 || V <= 0 || state == nullptr || decay_logit == nullptr || raw == nullptr) return DFI_ERR_SHAPE;
+    if (rows <= 0) return DFI_OK;
     if (dtype != DFI_DTYPE_F32 && dtype != DFI_DTYPE_BF16) return DFI_ERR_DTYPE;
     if (mode == 1 && bonus == nullptr) return DFI_ERR_SHAPE;
     if (mode == 0 && !(decay_param > 0.f)) return DFI_ERR_SHAPE;
@@ -288,14 +298,21 @@ DFI_EXPORT int dfi_linear_scan(int mode, const void* q, int q_stride, const void
     a.decay_param = decay_param; a.q_scale = q_scale;
     a.state = state; a.slot_stride = slot_stride; a.cu_rows = cu_rows; a.seq_slot = seq_slot;
     a.H = H; a.D = D; a.V = V;
-    a.norm_weight = norm_weight; a.norm_head_stride = norm_head_stride; a.eps = eps;
-    a.out = out; a.out_stride = out_stride; a.out_scale = out_scale;
+    a.raw = raw;
     a.carry_rows = carry_rows; a.carry_width = carry_width; a.carry_offset = carry_offset;
     a.bf16 = dtype == DFI_DTYPE_BF16;
     cudaStream_t st = (cudaStream_t)stream;
-    if (mode == 0) return pick_rows<0>(a, n_seqs, st);
-    if (mode == 1) return pick_rows<1>(a, n_seqs, st);
-    return DFI_ERR_SHAPE;
+    int rc = mode == 0 ? pick_rows<0>(a, n_seqs, st) : mode == 1 ? pick_rows<1>(a, n_seqs, st) : DFI_ERR_SHAPE;
+    if (rc != DFI_OK) return rc;
+    const dim3 grid(rows, (H + 3) / 4);
+    if (a.bf16)
+        launch(head_norm_gate_kernel<bf16>, grid, dim3(128), 0, st, (const float*)raw, H, V, norm_weight, norm_head_stride,
+               eps, (const bf16*)g, g_stride, out_scale, (bf16*)out, out_stride);
+    else
+        launch(head_norm_gate_kernel<float>, grid, dim3(128), 0, st, (const float*)raw, H, V, norm_weight, norm_head_stride,
+               eps, (const float*)g, g_stride, out_scale, (float*)out, out_stride);
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
 }
 
 DFI_EXPORT int dfi_token_shift(const void* h, const float* mu, int n_mix, int width, int rows, const float* state,

@@ -246,3 +246,23 @@ DFI_EXPORT int dfi_split_decode(const void* q, int q_row_stride, void* out, int 
     DFI_CHECK_LAUNCH();
     return DFI_OK;
 }
+
+// The merge alone: `partial` [n_seqs, n_q, n_parts, 2 + v_dim] (maximum in natural units, sum, weighted
+// values) as some other kernel left it; out [n_seqs, out_row_stride] in `dtype`, gated and scaled.
+DFI_EXPORT int dfi_split_merge(const float* partial, int n_seqs, int n_q, int v_dim, int n_parts, const void* gate,
+                               int gate_row_stride, float out_scale, void* out, int out_row_stride, int dtype,
+                               void* stream) {
+    if (n_seqs <= 0) return DFI_OK;
+    if (n_q <= 0 || v_dim <= 0 || n_parts <= 0 || partial == nullptr) return DFI_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid(n_seqs, (n_q + 3) / 4);
+    if (dtype == DFI_DTYPE_F32)
+        launch(split_merge_kernel<float>, grid, 128, 0, st, partial, n_q, v_dim, n_parts, (const float*)gate,
+               gate_row_stride, out_scale, (float*)out, out_row_stride);
+    else if (dtype == DFI_DTYPE_BF16)
+        launch(split_merge_kernel<bf16>, grid, 128, 0, st, partial, n_q, v_dim, n_parts, (const bf16*)gate,
+               gate_row_stride, out_scale, (bf16*)out, out_row_stride);
+    else return DFI_ERR_DTYPE;
+    DFI_CHECK_LAUNCH();
+    return DFI_OK;
+}

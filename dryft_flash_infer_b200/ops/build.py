@@ -34,6 +34,11 @@ CORE_SOURCES = ["elementwise.cu", "attention_generic.cu", "sampling.cu", "skinny
                 "wide_residual.cu", "split_attention.cu", "linear_scan.cu"]
 #: the tensor-core attention, built once per head size (-DDFI_HEAD_DIM=...)
 ATTENTION_SOURCES = ["attention_mma.cu", "attention_tcgen05.cu"]
+#: the tensor-core attention for keys and values of different sizes, built once per pair of sizes
+#: (-DDFI_KEY_DIM=... -DDFI_VALUE_DIM=...) at first use
+SPLIT_ATTENTION_SOURCES = ["attention_mma_split.cu"]
+#: the pairs compiled ahead by ``all_libraries``
+PREBUILT_SPLIT_DIMS = ((64, 128),)
 #: head sizes compiled ahead by ``all_libraries`` (others compile at first use)
 PREBUILT_HEAD_DIMS = (16, 32, 64, 128)
 #: host-only code (no CUDA calls, not linked against the driver): the safetensors reader
@@ -149,6 +154,9 @@ def all_libraries() -> list[tuple[str, list[str], list[str]]]:
     out = [("dfi_io", IO_SOURCES, []), ("dfi_plan", PLAN_SOURCES, []), ("dfi_core", CORE_SOURCES, [])]
     for dim in PREBUILT_HEAD_DIMS:
         out.append((f"dfi_attention_d{dim}", ATTENTION_SOURCES, [f"-DDFI_HEAD_DIM={dim}"]))
+    for key_dim, value_dim in PREBUILT_SPLIT_DIMS:
+        out.append((f"dfi_attention_k{key_dim}_v{value_dim}", SPLIT_ATTENTION_SOURCES,
+                    [f"-DDFI_KEY_DIM={key_dim}", f"-DDFI_VALUE_DIM={value_dim}"]))
     return out
 
 

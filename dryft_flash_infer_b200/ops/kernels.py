@@ -13,7 +13,7 @@ import weakref
 
 import torch
 
-from .build import ATTENTION_SOURCES, CORE_SOURCES, load_library
+from .build import ATTENTION_SOURCES, CORE_SOURCES, SPLIT_ATTENTION_SOURCES, load_library
 
 _ERRORS = {
     1: "unsupported dtype (kernels take float32 and bfloat16)",
@@ -407,6 +407,42 @@ def head_norm_write(proj: torch.Tensor, n_q: int, n_kv: int, head_dim: int, v_di
     return proj[:, : n_q * head_dim]
 
 
+def _split_attention_library(key_dim: int, value_dim: int):
+    return _with_pdl(load_library(f"dfi_attention_k{key_dim}_v{value_dim}", SPLIT_ATTENTION_SOURCES,
+                                  [f"-DDFI_KEY_DIM={key_dim}", f"-DDFI_VALUE_DIM={value_dim}"]),
+                     "dfi_attention_split_set_pdl")
+
+
+def split_prefill_takes(q: torch.Tensor, head_dim: int, v_dim: int) -> bool:
+    """True if ``attention_split_prefill`` takes these query rows: bfloat16, key and value sizes in steps of
+    16 (up to 256 and 128), rows that start on 16 bytes."""
+    return (q.is_cuda and q.dtype == torch.bfloat16 and head_dim % 16 == 0 and v_dim % 16 == 0 and head_dim <= 256
+            and v_dim <= 128 and q.stride(1) == 1 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+
+
+def attention_split_prefill(q: torch.Tensor, cache, ctx, n_q: int, n_kv: int, head_dim: int, scale: float,
+                            window: int = 0, gate: torch.Tensor | None = None, out_scale: float = 1.0,
+                            out: torch.Tensor | None = None) -> torch.Tensor:
+    """Tensor-core flash attention (bfloat16) for any number of query rows per sequence over keys of
+    ``head_dim`` and values of their own size (``csrc/attention_mma_split.cu``, built once per pair of
+    sizes at first use); ``gate`` / ``out_scale`` / ``out`` as in ``attention_generic``."""
+    _need_cuda(q, cache.k, gate)
+    rows, v_dim = q.shape[0], cache.v.shape[-1]
+    if not split_prefill_takes(q, head_dim, v_dim):
+        raise KernelError(f"attention_split_prefill: bfloat16 rows on 16 bytes, sizes in steps of 16, got {head_dim}/{v_dim}")
+    assert q.shape[1] == n_q * head_dim and cache.k.shape[-1] == head_dim and cache.k.dtype == torch.bfloat16
+    assert gate is None or (gate.dtype == q.dtype and gate.shape == (rows, n_q) and gate.stride(1) == 1)
+    if out is None:
+        out = torch.empty((rows, n_q * v_dim), dtype=q.dtype, device=q.device)
+    assert out.shape == (rows, n_q * v_dim) and out.stride(1) == 1 and out.dtype == q.dtype
+    _check(_split_attention_library(head_dim, v_dim).dfi_attention_split_prefill(
+        _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
+        cache.block_table.shape[1], _ptr(ctx.cu_rows), _ptr(ctx.seq_start), ctx.n_seqs, ctx.max_q_len, n_q, n_kv,
+        cache.page_size, cache.ring_tokens, window, _f(scale), _ptr(gate), gate.stride(0) if gate is not None else 0,
+        _f(out_scale), _stream()), "attention_split_prefill", f"sizes {head_dim}/{v_dim}, {n_q}/{n_kv} heads")
+    return out
+
+
 _SPLIT_SCRATCH: dict = {}
 
 
@@ -423,7 +459,8 @@ def attention_split_decode(q: torch.Tensor, cache, ctx, n_q: int, n_kv: int, hea
     """Attention for a step of one query row per sequence (row ``i`` is sequence ``i``), either dtype, any
     head size up to 256 and values of a size of their own: every sequence's keys are cut into ``n_parts``
     parts that run at once and are merged by a second kernel, which also applies ``sigmoid(gate)`` per
-    head and ``out_scale`` (see ``attention_generic``)."""
+    head and ``out_scale`` (see ``attention_generic``).  bfloat16 with sizes in steps of 16 runs the parts on
+    tensor cores (``csrc/attention_mma_split.cu``), everything else on the float32 pipes."""
     _need_cuda(q, cache.k, gate)
     rows, v_dim = q.shape[0], cache.v.shape[-1]
     assert rows == ctx.n_seqs and q.stride(1) == 1 and q.shape[1] == n_q * head_dim and cache.k.shape[-1] == head_dim
@@ -440,10 +477,20 @@ def attention_split_decode(q: torch.Tensor, cache, ctx, n_q: int, n_kv: int, hea
     assert out.shape == (rows, n_q * v_dim) and out.stride(1) == 1 and out.dtype == q.dtype
     global LAUNCHES
     LAUNCHES += 1                                # the call launches two kernels
+    gate_stride = gate.stride(0) if gate is not None else 0
+    if split_prefill_takes(q, head_dim, v_dim) and n_q // n_kv <= 16:
+        # bfloat16 on tensor cores: the group's heads are the rows of one tile, a page is read once for all of them
+        _check(_split_attention_library(head_dim, v_dim).dfi_attention_split_decode(
+            _ptr(q), q.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table), cache.block_table.shape[1],
+            _ptr(ctx.seq_start), rows, n_q, n_kv, cache.page_size, cache.ring_tokens, window, _f(scale), n_parts,
+            _ptr(held[0]), _stream()), "attention_split_decode", f"head sizes {head_dim}/{v_dim}")
+        _check(lib.dfi_split_merge(_ptr(held[0]), rows, n_q, v_dim, n_parts, _ptr(gate), gate_stride, _f(out_scale),
+                                   _ptr(out), out.stride(0), _code(q), _stream()), "attention_split_decode (merge)")
+        return out
     _check(lib.dfi_split_decode(
         _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cache.k), _ptr(cache.v), _ptr(cache.block_table),
         cache.block_table.shape[1], _ptr(ctx.seq_start), rows, n_q, n_kv, head_dim, v_dim, cache.page_size,
-        cache.ring_tokens, window, _f(scale), _ptr(gate), gate.stride(0) if gate is not None else 0, _f(out_scale),
+        cache.ring_tokens, window, _f(scale), _ptr(gate), gate_stride, _f(out_scale),
         n_parts, _ptr(held[0]), _code(q), _stream()), "attention_split_decode", f"head sizes {head_dim}/{v_dim}")
     return out
 
@@ -456,7 +503,8 @@ def linear_scan(mode: int, q, k, v, gate, decay_logit: torch.Tensor, decay_bias,
                 norm_per_head: bool, eps: float, out: torch.Tensor, out_scale: float = 1.0, carry_rows=None,
                 carry_offset: int = 0) -> torch.Tensor:
     """The recurrence of a matrix state ``S [key_dim, value_dim]`` per (sequence, head) over the step's rows,
-    in float32, in the order of the tokens (``csrc/linear_scan.cu``).
+    in float32, in the order of the tokens (``csrc/linear_scan.cu``): one CTA per (sequence, head, 32 columns of
+    ``S``), then a kernel of one warp per (row, head) for the norm and the gate.
 
     ``SCAN_DECAY_THEN_READ``: ``S = diag(a) S + k v^T; o = S^T q`` with ``a = sigmoid(z)^(1/decay_param)``;
     ``SCAN_READ_THEN_DECAY``: ``o = (S + diag(bonus) k v^T)^T q; S = diag(a) S + k v^T`` with
@@ -483,14 +531,16 @@ def linear_scan(mode: int, q, k, v, gate, decay_logit: torch.Tensor, decay_bias,
         assert carry_rows.dtype == out.dtype and carry_rows.is_contiguous() and carry_rows.shape[0] == rows
         carry_width = carry_rows.shape[1]
         assert carry_offset + carry_width <= state.shape[1]
-    if key_dim > 256 or value_dim > 256 or key_dim * value_dim > 128 * 256:
-        raise KernelError(f"linear_scan: a state of {key_dim} x {value_dim} per head is more than the kernel keeps "
-                          f"in registers (at most 256 x 128 or 128 x 256)")
+    if key_dim > 256:
+        raise KernelError(f"linear_scan: {key_dim} key channels per head are more than the kernel keeps in registers (256)")
+    raw = torch.empty((rows, n_heads * value_dim), dtype=torch.float32, device=out.device)
+    global LAUNCHES
+    LAUNCHES += 1                                # the call launches two kernels: the recurrence, then norm and gate
     _check(_core().dfi_linear_scan(
         int(mode), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(gate), gate.stride(0),
         _ptr(decay_logit), _ptr(decay_bias), _ptr(bonus), _f(decay_param), _f(q_scale), _ptr(state),
-        ctypes.c_longlong(state.stride(0)), _ptr(ctx.cu_rows), _ptr(ctx.seq_slot), ctx.n_seqs, n_heads, key_dim,
-        value_dim, _ptr(norm_weight), value_dim if norm_per_head else 0, _f(eps), _ptr(out), out.stride(0),
+        ctypes.c_longlong(state.stride(0)), _ptr(ctx.cu_rows), _ptr(ctx.seq_slot), ctx.n_seqs, rows, n_heads, key_dim,
+        value_dim, _ptr(norm_weight), value_dim if norm_per_head else 0, _f(eps), _ptr(raw), _ptr(out), out.stride(0),
         _f(out_scale), _ptr(carry_rows), carry_width, ctypes.c_longlong(carry_offset), _code(out), _stream()),
         "linear_scan", f"state {key_dim} x {value_dim}")
     return out

@@ -58,6 +58,22 @@ class GatedAttention(Mixer):
             out["k_norm"] = TensorDecl((self.head_dim,), "k_norm", init="norm", precision="float32")
         return out
 
+    @property
+    def _used_rows(self) -> int:
+        return (self.n_heads + self.n_kv_heads) * self.head_dim + self.n_kv_heads * self.v_head_dim + self.n_heads
+
+    def buffer_shapes(self):
+        # the fused projection's rows are rounded up to eight, so that a row of its result starts on 16 bytes
+        # (what the tensor-core attention's copies of the query rows need); the spare rows are zeros
+        shapes = super().buffer_shapes()
+        (rows, cols), precision = shapes["qkvg"]
+        shapes["qkvg"] = ((-(-rows // 8) * 8, cols), precision)
+        return shapes
+
+    def bind(self, buffers) -> None:
+        super().bind(buffers)
+        self.qkvg[self._used_rows:].zero_()
+
     def cache_need(self):
         return KVNeed(self.n_kv_heads, self.head_dim, self.window,
                       self.v_head_dim if self.v_head_dim != self.head_dim else 0)
@@ -70,10 +86,13 @@ class GatedAttention(Mixer):
         proj = kernels.linear(x, self.qkvg)
         q = kernels.head_norm_write(proj, H, G, D, V, self.q_norm, self.k_norm, self.qk_norm_eps, ctx.row_pos,
                                     ctx.row_seq, cache)
-        gates = proj[:, (H + G) * D + G * V:]
+        gates = proj[:, self._used_rows - H: self._used_rows]
         if ctx.all_decode:
             return kernels.attention_split_decode(q, cache, ctx, H, G, D, self.scale, self.window, gate=gates,
                                                   out_scale=scale, out=out)
+        if kernels.split_prefill_takes(q, D, V):
+            return kernels.attention_split_prefill(q, cache, ctx, H, G, D, self.scale, self.window, gate=gates,
+                                                   out_scale=scale, out=out)
         return kernels.attention_generic(q, cache, ctx.row_seq, ctx.row_pos, H, G, D, self.scale, self.window,
                                          gate=gates, out_scale=scale, out=out)
 

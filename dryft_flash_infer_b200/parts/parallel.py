@@ -69,6 +69,15 @@ class ParallelMixer(Mixer):
                     out[f"{name}.{local}"] = dataclasses.replace(decl, buffer=f"{name}.{decl.buffer}")
         return out
 
+    def buffer_shapes(self):
+        out = {"o": ((self.hidden_size, self.inner_size), "compute")}
+        for name, branch in zip(self.names, self.branches):
+            joint = branch.tensors()[branch.output_tensor].buffer
+            for buffer, shape in branch.buffer_shapes().items():
+                if buffer != joint:
+                    out[f"{name}.{buffer}"] = shape         # a branch may ask for more than its tensors fill
+        return out
+
     def bind(self, buffers) -> None:
         self.o = buffers["o"]
         for name, branch in zip(self.names, self.branches):

@@ -211,16 +211,20 @@ def test_token_shift_reads_the_row_before_or_the_kept_one(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n_q, n_kv, dim, vdim", [(4, 2, 16, 24), (3, 3, 20, 12), (4, 1, 8, 36), (8, 2, 48, 80)])
+@pytest.mark.parametrize("n_q, n_kv, dim, vdim", [(4, 2, 16, 24), (3, 3, 20, 12), (4, 1, 8, 36), (8, 2, 48, 80),
+                                                  (6, 2, 32, 64), (2, 1, 128, 128), (2, 2, 256, 16)])
 def test_attention_with_values_of_their_own_size(n_q, n_kv, dim, vdim, dtype):
-    """Norm and cache write, then every row's attention over scrambled pages: prompt rows by the row kernel,
-    single rows by the kernel that deals a sequence's keys to several CTAs; gates and the constant applied."""
+    """Norm and cache write, then every row's attention over scrambled pages: prompt rows by the row kernel
+    and, in bfloat16 with sizes in steps of 16, by the tensor-core kernel (also for a portion that starts
+    inside a page); single rows by the kernel that deals a sequence's keys to several CTAs; gates and the
+    constant applied."""
     from dryft_flash_infer_b200.cache.storage import LayerCache
     from dryft_flash_infer_b200.ops import kernels
 
     torch.manual_seed(n_q + dim)
     lengths, eps, scale = [130, 1, 67], 1e-5, 0.3
-    width = (n_q + n_kv) * dim + n_kv * vdim + n_q
+    used = (n_q + n_kv) * dim + n_kv * vdim + n_q
+    width = -(-used // 8) * 8                                   # rows start on 16 bytes, as the mixer's do
     pages = 1 + sum(-(-n // 64) for n in lengths)
     order = (1 + torch.randperm(pages - 1)).tolist()
     table = torch.zeros(3, 4, dtype=torch.int32)
@@ -235,7 +239,18 @@ def test_attention_with_values_of_their_own_size(n_q, n_kv, dim, vdim, dtype):
     row_pos = torch.cat([torch.arange(n) for n in lengths]).to(torch.int32)
     dev = proj.clone().cuda()
     q = kernels.head_norm_write(dev, n_q, n_kv, dim, vdim, qw.cuda(), kw.cuda(), eps, row_pos.cuda(), row_seq.cuda(), cache)
-    gates = dev[:, (n_q + n_kv) * dim + n_kv * vdim:]
+    gates = dev[:, used - n_q: used]
+    fast = None
+    if kernels.split_prefill_takes(q, dim, vdim):
+        whole = SimpleNamespace(n_seqs=3, max_q_len=max(lengths), seq_start=torch.zeros(3, dtype=torch.int32).cuda(),
+                                cu_rows=torch.tensor(np.concatenate([[0], np.cumsum(lengths)]), dtype=torch.int32).cuda())
+        fast = kernels.attention_split_prefill(q, cache, whole, n_q, n_kv, dim, scale, gate=gates, out_scale=0.7).float().cpu()
+        tail = SimpleNamespace(n_seqs=1, max_q_len=70, seq_start=torch.tensor([60], dtype=torch.int32).cuda(),
+                               cu_rows=torch.tensor([0, 70], dtype=torch.int32).cuda())
+        fast_tail = kernels.attention_split_prefill(q[60:130], cache, tail, n_q, n_kv, dim, scale, gate=gates[60:130],
+                                                    out_scale=0.7).float().cpu()
+    else:
+        assert dtype == torch.float32 or dim % 16 or vdim % 16
     got = kernels.attention_generic(q, cache, row_seq.cuda(), row_pos.cuda(), n_q, n_kv, dim, scale, gate=gates,
                                     out_scale=0.7).float().cpu()
     # the last row of every sequence once more, as a decode step sees it
@@ -253,7 +268,7 @@ def test_attention_with_values_of_their_own_size(n_q, n_kv, dim, vdim, dtype):
         if dtype == torch.bfloat16:
             qq, kk = qq.to(dtype).double(), kk.to(dtype).double()          # what the cache and the query rows hold
         vv = rows[:, (n_q + n_kv) * dim:(n_q + n_kv) * dim + n_kv * vdim].view(n, n_kv, vdim)
-        gg = torch.sigmoid(rows[:, -n_q:])
+        gg = torch.sigmoid(rows[:, used - n_q: used])
         for head in range(n_q):
             kv = head // (n_q // n_kv)
             scores = (qq[:, head] @ kk[:, kv].T) * scale
@@ -263,6 +278,9 @@ def test_attention_with_values_of_their_own_size(n_q, n_kv, dim, vdim, dtype):
     want = want.reshape(sum(lengths), n_q * vdim).float()
     tol = 2e-5 if dtype == torch.float32 else 0.03
     assert (got - want).abs().max() <= tol * (1 + want.abs().max())
+    if fast is not None:
+        assert (fast - want).abs().max() <= tol * (1 + want.abs().max()), "tensor-core kernel, whole prompts"
+        assert (fast_tail - want[60:130]).abs().max() <= tol * (1 + want.abs().max()), "tensor-core kernel, a portion"
     for parts, rows in single.items():
         assert (rows - want[last]).abs().max() <= tol * (1 + want.abs().max()), f"{parts} parts"
 
