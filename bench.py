@@ -285,7 +285,8 @@ def qwen_like(width: int, layers: int, vocab: int) -> dict:
 
 def timed(fn, repeats: int = 5, flush=None):
     """Median device time of ``fn()`` in microseconds, by CUDA events, after two untimed calls; ``flush`` (a
-    buffer larger than L2) is rewritten before every timed call."""
+    buffer larger than L2) is rewritten before every timed call.  For work of a millisecond or more: the
+    host's part of a call (tens of microseconds) is inside the events."""
     import torch
 
     times = []
@@ -303,22 +304,57 @@ def timed(fn, repeats: int = 5, flush=None):
     return statistics.median(times)
 
 
+def timed_kernel(make, replicas: int, repeats: int = 5) -> float:
+    """Device time in microseconds of one call of a kernel, without the host: ``make(i)`` returns the call on the
+    ``i``-th copy of its inputs (``replicas`` copies, together larger than L2, so that no call finds the data
+    of the call before in the cache); all calls are captured in one CUDA graph, whose replay is timed by CUDA
+    events and divided by the number of calls."""
+    import torch
+
+    calls = [make(i) for i in range(replicas)]
+    for call in calls:
+        call()                                   # untimed: sizes scratch buffers, loads the libraries
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for call in calls:
+            call()
+    times = []
+    for i in range(3 + repeats):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(a.elapsed_time(b) * 1e3 / replicas)
+    return statistics.median(times)
+
+
 def sasilorn_kernels(width: int, tokens: int, batch: int, context: int, peak: dict) -> dict:
     """The hot kernels of the new design by themselves, beside the like kernels of Qwen3, each with its roofline
     fraction: attention over a prompt (tensor cores), attention for one token a sequence (cache bytes), the
-    state recurrence over a prompt (float32 pipes) and for one token (state bytes), and the norms (row bytes)."""
-    import numpy as np
+    state recurrence over prompts (float32 pipes: 7 operations per token and element of the state) and for one
+    token (state bytes), and the norms (row bytes).  Timed by ``timed_kernel``: inputs larger than L2."""
     import torch
     from types import SimpleNamespace
     from dryft_flash_infer_b200.cache.storage import LayerCache
     from dryft_flash_infer_b200.ops import kernels
 
     dev, bf = "cuda", torch.bfloat16
-    flush = torch.zeros(160 << 20, dtype=torch.float32, device=dev)             # 640 MB: L2 holds 126 MB
     heads, kv, d = width // 128, max(1, width // 512), 128
     out = {}
-    tflops = lambda flops, us: flops / (us * 1e-6) / 1e12
-    gbs = lambda nbytes, us: nbytes / (us * 1e-6) / 1e9
+
+    def compute(name, flops, us, kernel, unit="tflops", peak_value=None):
+        rate = flops / (us * 1e-6) / 1e12
+        out[name] = {"us": round(us, 1), unit: round(rate, 2), "kernel": kernel}
+        if peak_value:
+            out[name]["frac"] = round(rate / peak_value, 4)
+
+    def memory(name, nbytes, us, kernel):
+        rate = nbytes / (us * 1e-6) / 1e9
+        out[name] = {"us": round(us, 1), "gbs": round(rate, 1), "frac": round(rate / peak["hbm_gbs"], 4), "kernel": kernel}
 
     def paged(n_seqs, length, dk, dv):
         pages = -(-length // 64)
@@ -327,68 +363,68 @@ def sasilorn_kernels(width: int, tokens: int, batch: int, context: int, peak: di
         v = torch.randn(1 + n_seqs * pages, kv, 64, dv, device=dev).to(bf)
         return LayerCache(k, v, table, 64, 0, True)
 
-    # attention over a prompt of `tokens`: ours (keys 128, values 128) and Qwen3's tcgen05 kernel (128)
-    cache = paged(1, tokens, d, d)
-    q = torch.randn(tokens, heads * d, device=dev).to(bf)
+    def copies(n, make):
+        return [make() for _ in range(n)]
+
+    # attention over a prompt of `tokens` (heads of 128 / 128): ours, Qwen3's tcgen05 kernel, and the mma.sync
+    # kernel that Qwen3-style models of other head sizes run
+    n = 12
+    caches = copies(n, lambda: paged(1, tokens, d, d))
+    qs = copies(n, lambda: torch.randn(tokens, heads * d, device=dev).to(bf))
     gate = torch.randn(tokens, heads, device=dev).to(bf)
     ctx = SimpleNamespace(n_seqs=1, max_q_len=tokens, seq_start=torch.zeros(1, dtype=torch.int32, device=dev),
                           cu_rows=torch.tensor([0, tokens], dtype=torch.int32, device=dev))
     flops = 4.0 * heads * d * tokens * tokens / 2
-    us = timed(lambda: kernels.attention_split_prefill(q, cache, ctx, heads, kv, d, d ** -0.5, gate=gate), flush=flush)
-    out["attention_prompt"] = {"us": round(us, 1), "tflops": round(tflops(flops, us), 1),
-                               "frac": round(tflops(flops, us) / peak["bf16_tflops"], 4), "kernel": "attention_split_prefill (mma.sync)"}
-    us = timed(lambda: kernels.attention_prefill_tc(q, cache, ctx, heads, kv, d, d ** -0.5), flush=flush)
-    out["attention_prompt_qwen3"] = {"us": round(us, 1), "tflops": round(tflops(flops, us), 1),
-                                     "frac": round(tflops(flops, us) / peak["bf16_tflops"], 4), "kernel": "attention_prefill_tc (tcgen05)"}
-    us = timed(lambda: kernels.attention_prefill(q, cache, ctx, heads, kv, d, d ** -0.5), flush=flush)
-    out["attention_prompt_qwen3_other_head_sizes"] = {"us": round(us, 1), "tflops": round(tflops(flops, us), 1),
-                                                      "frac": round(tflops(flops, us) / peak["bf16_tflops"], 4), "kernel": "attention_prefill (mma.sync)"}
+    us = timed_kernel(lambda i: lambda: kernels.attention_split_prefill(qs[i], caches[i], ctx, heads, kv, d, d ** -0.5, gate=gate), n)
+    compute("attention_prompt", flops, us, "attention_split_prefill (mma.sync, gate in the epilogue)", peak_value=peak["bf16_tflops"])
+    us = timed_kernel(lambda i: lambda: kernels.attention_prefill_tc(qs[i], caches[i], ctx, heads, kv, d, d ** -0.5), n)
+    compute("attention_prompt_qwen3", flops, us, "attention_prefill_tc (tcgen05)", peak_value=peak["bf16_tflops"])
+    us = timed_kernel(lambda i: lambda: kernels.attention_prefill(qs[i], caches[i], ctx, heads, kv, d, d ** -0.5), n)
+    compute("attention_prompt_qwen3_other_head_sizes", flops, us, "attention_prefill (mma.sync)", peak_value=peak["bf16_tflops"])
+    del caches, qs
     # attention for one token of `batch` sequences at `context`
-    cache = paged(batch, context, d, d)
+    n = 8
+    caches = copies(n, lambda: paged(batch, context, d, d))
     q1 = torch.randn(batch, heads * d, device=dev).to(bf)
     g1 = torch.randn(batch, heads, device=dev).to(bf)
     dctx = SimpleNamespace(n_seqs=batch, max_kv_len=context, decode_plans=None,
                            seq_start=torch.full((batch,), context - 1, dtype=torch.int32, device=dev))
     nbytes = batch * context * kv * 2 * d * 2
-    us = timed(lambda: kernels.attention_split_decode(q1, cache, dctx, heads, kv, d, d ** -0.5, gate=g1), flush=flush)
-    out["attention_token"] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
-                              "kernel": "split_decode + merge"}
-    us = timed(lambda: kernels.attention_decode(q1, cache, dctx, heads, kv, d, d ** -0.5), flush=flush)
-    out["attention_token_qwen3"] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
-                                    "kernel": "attention_decode (mma.sync, stream-K)"}
+    us = timed_kernel(lambda i: lambda: kernels.attention_split_decode(q1, caches[i], dctx, heads, kv, d, d ** -0.5, gate=g1), n)
+    memory("attention_token", nbytes, us, "attention_split_decode (mma.sync) + merge with the gate")
+    us = timed_kernel(lambda i: lambda: kernels.attention_decode(q1, caches[i], dctx, heads, kv, d, d ** -0.5), n)
+    memory("attention_token_qwen3", nbytes, us, "attention_decode (mma.sync, one kernel)")
+    del caches
     # the state recurrence: time mixing with heads of 64 x 64
     H, D, V = width // 64, 64, 64
-    for name, rows, n_seqs in (("scan_prompt", tokens, 1), ("scan_token", batch, batch)):
-        r, k, v, g = (torch.randn(rows, H * D, device=dev).to(bf) for _ in range(4))
-        z = torch.randn(rows, H * D, device=dev) - 1.0
+    for name, per, n_seqs, n in (("scan_prompt", tokens, 1, 4), ("scan_prompt_batch4", tokens, 4, 2), ("scan_token", 1, batch, 28)):
+        rows = per * n_seqs
+        r, k, v, g = (copies(n, lambda: torch.randn(rows, H * D, device=dev).to(bf)) for _ in range(4))
+        z = copies(n, lambda: torch.randn(rows, H * D, device=dev) - 1.0)
         w0, u, norm = torch.zeros(H * D, device=dev), torch.randn(H * D, device=dev), torch.ones(H * V, device=dev)
-        state = torch.zeros(n_seqs, H * D * V, device=dev)
+        states = copies(n, lambda: torch.zeros(n_seqs, H * D * V, device=dev))
         res = torch.empty(rows, H * V, device=dev, dtype=bf)
-        per = rows // n_seqs
         sctx = SimpleNamespace(n_seqs=n_seqs, cu_rows=torch.arange(0, rows + 1, per, dtype=torch.int32, device=dev),
                                seq_slot=torch.arange(n_seqs, dtype=torch.int32, device=dev))
-        us = timed(lambda: kernels.linear_scan(kernels.SCAN_READ_THEN_DECAY, r, k, v, g, z, w0, u, 0.0, 1.0, state, sctx, H, D, V,
-                                               norm, True, 1e-5, res), flush=flush)
-        if n_seqs == 1:
-            flops = 7.0 * rows * H * D * V
-            out[name] = {"us": round(us, 1), "fp32_tflops": round(tflops(flops, us), 2), "tokens": rows,
-                         "us_per_token": round(us / rows, 4), "kernel": "linear_scan (float32 pipes, in the order of the tokens)"}
+        us = timed_kernel(lambda i: lambda: kernels.linear_scan(kernels.SCAN_READ_THEN_DECAY, r[i], k[i], v[i], g[i], z[i], w0, u,
+                                                                0.0, 1.0, states[i], sctx, H, D, V, norm, True, 1e-5, res), n)
+        if per > 1:
+            compute(name, 7.0 * rows * H * D * V, us, "linear_scan + head_norm_gate (float32 pipes, in the order of the tokens)",
+                    unit="fp32_tflops")
+            out[name].update(sequences=n_seqs, us_per_token=round(us / per, 4), ctas=n_seqs * H * (V // 32))
         else:
-            nbytes = 2 * n_seqs * H * D * V * 4
-            out[name] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
-                         "kernel": "linear_scan"}
+            memory(name, 2 * n_seqs * H * D * V * 4, us, "linear_scan + head_norm_gate")
+        del r, k, v, g, z, states
     # the norms over a prompt's rows
-    x32, delta = torch.randn(tokens, width, device=dev), torch.randn(tokens, width, device=dev).to(bf)
+    n = 8
+    x32 = copies(n, lambda: torch.randn(tokens, width, device=dev))
+    x16 = copies(n, lambda: torch.randn(tokens, width, device=dev).to(bf))
+    deltas = copies(n, lambda: torch.randn(tokens, width, device=dev).to(bf))
     one, w, b = torch.ones(1, device=dev), torch.ones(width, device=dev), torch.zeros(width, device=dev)
-    us = timed(lambda: kernels.dynamic_tanh(x32, delta, one, w, b, bf), flush=flush)
-    nbytes = tokens * width * (4 + 4 + 2 + 2)
-    out["norm_prompt"] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
-                          "kernel": "dynamic_tanh with the float32 residual add"}
-    x16 = torch.randn(tokens, width, device=dev).to(bf)
-    us = timed(lambda: kernels.add_rms_norm(x16, delta, w, 1e-6), flush=flush)
-    nbytes = tokens * width * (2 + 2 + 2 + 2)
-    out["norm_prompt_qwen3"] = {"us": round(us, 1), "gbs": round(gbs(nbytes, us), 1), "frac": round(gbs(nbytes, us) / peak["hbm_gbs"], 4),
-                                "kernel": "rmsnorm with the bfloat16 residual add"}
+    us = timed_kernel(lambda i: lambda: kernels.dynamic_tanh(x32[i], deltas[i], one, w, b, bf), n)
+    memory("norm_prompt", tokens * width * (4 + 4 + 2 + 2), us, "dynamic_tanh with the float32 residual add")
+    us = timed_kernel(lambda i: lambda: kernels.add_rms_norm(x16[i], deltas[i], w, 1e-6), n)
+    memory("norm_prompt_qwen3", tokens * width * (2 + 2 + 2 + 2), us, "rmsnorm with the bfloat16 residual add")
     return out
 
 

@@ -12,11 +12,12 @@
 //
 // One CTA of eight warps owns one (sequence, head, 32 columns of S) for all the tokens the step brings
 // it: a column of S needs no other column, so a head spreads over V / 32 CTAs.  Warp w keeps rows
-// [w NI, (w+1) NI) of its columns in registers, lane c column c.  Tokens are taken sixteen at a time: their
-// q, k, decays and v wait in shared memory as float32 (the decay computed once per token and channel);
-// while the sixteen are worked through, the next sixteen are already on their way from global memory into
-// registers.  Every warp leaves its rows' share of o_t in shared memory; after the sixteen tokens the
-// shares are summed and stored as float32.  A second kernel, one warp per (row, head), divides a head's
+// [w NI, (w+1) NI) of its columns in registers, lane c column c.  Tokens are fetched up to 64 at a time: their
+// q, k, decays and v wait in shared memory as float32 (the decay computed once per token and channel), and
+// while they are worked through the next ones are already on their way from global memory into registers:
+// with few CTAs per SM the latency of those loads, not the arithmetic, is what a token costs, so a fetch
+// has to cover many tokens.  Every warp leaves its rows' share of o_t in shared memory; after every
+// sixteen tokens the shares are summed and stored as float32.  A second kernel, one warp per (row, head), divides a head's
 // output by its root mean square, weights it, gates it with silu(g) and stores it in the storage type.
 //
 // The token shift of the time-mixing layer (every projection reads its own blend of a token's row and
@@ -73,43 +74,51 @@ __device__ __forceinline__ float decay_of(float z, float param) {
     return expf(-expf(z));
 }
 
+// Tokens per fetch of a prompt's rows: as many as shared memory and the registers of the fetch allow while
+// two CTAs still fit an SM for the narrow heads.  Steps of at most 16 rows a sequence (decoding, short
+// portions) fetch 16: few registers, so that many (sequence, head) pairs run at once.
+__host__ __device__ constexpr int scan_fetch_tokens(int ni) { return ni <= 16 ? 32 : 16; }
+
 // What a thread fetches for the chunk of up to TC tokens at row c0: elements tid, tid + THREADS, ... of
 // [TC][DP] (q, k, decay logits) and of [TC][32] (v); zeros past the chunk's tokens and the head's sizes.
-template <int TC, int DP, int PER, int PER_V>
+template <typename T, int TC, int DP, int PER, int PER_V>
 __device__ __forceinline__ void scan_fetch(const ScanArgs& a, int c0, int row1, int head, int j, int tid,
-                                           float (&fq)[PER], float (&fk)[PER], float (&fz)[PER], float (&fv)[PER_V]) {
+                                           T (&fq)[PER], T (&fk)[PER], float (&fz)[PER], T (&fv)[PER_V]) {
+    // Every load is issued whatever its index (clamped into the chunk and the head) and nothing is done with
+    // its value here: one straight run of loads, whose latencies overlap; what lies outside is set to zero
+    // when the values are moved to shared memory.
     constexpr int THREADS = kScanWarps * 32;
-    const int nt = min(TC, row1 - c0), D = a.D, V = a.V, HD = a.H * a.D;
+    const int last = min(TC, row1 - c0) - 1, D = a.D, V = a.V, HD = a.H * a.D;
+    const T* q = reinterpret_cast<const T*>(a.q);
+    const T* k = reinterpret_cast<const T*>(a.k);
+    const T* v = reinterpret_cast<const T*>(a.v);
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
-        const int idx = tid + e * THREADS, t = idx / DP, i = idx - t * DP;
-        fq[e] = 0.f; fk[e] = 0.f; fz[e] = 0.f;
-        if (t < nt && i < D) {
-            const size_t row = (size_t)(c0 + t);
-            const int col = head * D + i;
-            fq[e] = load_as_float(a.q, row * a.q_stride + col, a.bf16);
-            fk[e] = load_as_float(a.k, row * a.k_stride + col, a.bf16);
-            fz[e] = __ldg(a.decay_logit + row * HD + col);
-        }
+        const int idx = tid + e * THREADS, t = min(idx / DP, last), i = min(idx % DP, D - 1);
+        const size_t row = (size_t)(c0 + t);
+        const int col = head * D + i;
+        fq[e] = __ldg(q + row * a.q_stride + col);
+        fk[e] = __ldg(k + row * a.k_stride + col);
+        fz[e] = __ldg(a.decay_logit + row * HD + col);
     }
 #pragma unroll
     for (int e = 0; e < PER_V; ++e) {
-        const int idx = tid + e * THREADS, t = idx >> 5;
-        fv[e] = (t < nt && j < V) ? load_as_float(a.v, (size_t)(c0 + t) * a.v_stride + head * V + j, a.bf16) : 0.f;
+        const int idx = tid + e * THREADS, t = min(idx >> 5, last);
+        fv[e] = __ldg(v + (size_t)(c0 + t) * a.v_stride + head * V + min(j, V - 1));
     }
 }
 
-template <int MODE, int NI>
-__global__ void __launch_bounds__(kScanWarps * 32) linear_scan_kernel(const ScanArgs a) {
-    constexpr int TC = NI >= 32 ? kScanTokens / 2 : kScanTokens;      // the widest heads take eight tokens at a time
+template <typename T, int MODE, int NI, int TC>
+__global__ void __launch_bounds__(kScanWarps * 32, (NI <= 8 ? 2 : 1)) linear_scan_kernel(const ScanArgs a) {
     constexpr int DP = kScanWarps * NI, THREADS = kScanWarps * 32;
     constexpr int PER = TC * DP / THREADS;            // elements of q, k, z a thread fetches per chunk
     constexpr int PER_V = TC * 32 / THREADS;          // and of v
-    __shared__ __align__(16) float rs[TC * DP];
-    __shared__ __align__(16) float ks[TC * DP];
-    __shared__ __align__(16) float ws[TC * DP];
-    __shared__ float vs[TC * 32];
-    __shared__ float op[TC * kScanWarps * 32];
+    extern __shared__ __align__(16) float smem[];
+    float* rs = smem;                                 // [TC][DP]
+    float* ks = rs + TC * DP;                         // [TC][DP]
+    float* ws = ks + TC * DP;                         // [TC][DP]
+    float* vs = ws + TC * DP;                         // [TC][32]
+    float* op = vs + TC * 32;                         // [kScanTokens][warps][32]
     pdl_launch_next();
     pdl_wait();
     const int seq = blockIdx.x, head = blockIdx.y;
@@ -129,7 +138,8 @@ __global__ void __launch_bounds__(kScanWarps * 32) linear_scan_kernel(const Scan
         S[n] = (i < D && j < V) ? S_g[(size_t)i * V + j] : 0.f;
     }
 
-    float fq[PER], fk[PER], fz[PER], fv[PER_V];
+    T fq[PER], fk[PER], fv[PER_V];
+    float fz[PER];
     float bias[PER];
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
@@ -137,55 +147,63 @@ __global__ void __launch_bounds__(kScanWarps * 32) linear_scan_kernel(const Scan
         bias[e] = (a.decay_bias != nullptr && i < D) ? a.decay_bias[head * D + i] : 0.f;
     }
 
-    scan_fetch<TC, DP, PER, PER_V>(a, row0, row1, head, j, tid, fq, fk, fz, fv);
+    scan_fetch<T, TC, DP, PER, PER_V>(a, row0, row1, head, j, tid, fq, fk, fz, fv);
     for (int c0 = row0; c0 < row1; c0 += TC) {
         const int nt = min(TC, row1 - c0);
         __syncthreads();                               // the chunk before is done with shared memory
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
             const int idx = tid + e * THREADS, i = idx % DP;
-            rs[idx] = fq[e] * a.q_scale;
-            ks[idx] = fk[e];
-            ws[idx] = i < D ? decay_of<MODE>(fz[e] + bias[e], a.decay_param) : 1.f;
+            const bool live = i < D && idx / DP < nt;
+            rs[idx] = live ? to_float(fq[e]) * a.q_scale : 0.f;
+            ks[idx] = live ? to_float(fk[e]) : 0.f;
+            ws[idx] = live ? decay_of<MODE>(fz[e] + bias[e], a.decay_param) : 1.f;
         }
 #pragma unroll
-        for (int e = 0; e < PER_V; ++e) vs[tid + e * THREADS] = fv[e];
+        for (int e = 0; e < PER_V; ++e) {
+            const int idx = tid + e * THREADS;
+            vs[idx] = (j < V && (idx >> 5) < nt) ? to_float(fv[e]) : 0.f;
+        }
         __syncthreads();
         if (c0 + TC < row1)                            // on its way while this chunk is worked through
-            scan_fetch<TC, DP, PER, PER_V>(a, c0 + TC, row1, head, j, tid, fq, fk, fz, fv);
+            scan_fetch<T, TC, DP, PER, PER_V>(a, c0 + TC, row1, head, j, tid, fq, fk, fz, fv);
+        for (int s0 = 0; s0 < nt; s0 += kScanTokens) {
+            const int ns = min(kScanTokens, nt - s0);
 #pragma unroll 2
-        for (int t = 0; t < nt; ++t) {
-            const float vj = vs[t * 32 + lane];
-            float o = 0.f;
-            const float4* r4 = reinterpret_cast<const float4*>(rs + t * DP + i0);
-            const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP + i0);
-            const float4* w4 = reinterpret_cast<const float4*>(ws + t * DP + i0);
+            for (int t = s0; t < s0 + ns; ++t) {
+                const float vj = vs[t * 32 + lane];
+                float o = 0.f;
+                const float4* r4 = reinterpret_cast<const float4*>(rs + t * DP + i0);
+                const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP + i0);
+                const float4* w4 = reinterpret_cast<const float4*>(ws + t * DP + i0);
 #pragma unroll
-            for (int n4 = 0; n4 < NI / 4; ++n4) {
-                const float4 rv = r4[n4], kv4 = k4[n4], wv = w4[n4];
-                const float r[4] = {rv.x, rv.y, rv.z, rv.w}, k[4] = {kv4.x, kv4.y, kv4.z, kv4.w}, w[4] = {wv.x, wv.y, wv.z, wv.w};
+                for (int n4 = 0; n4 < NI / 4; ++n4) {
+                    const float4 rv = r4[n4], kv4 = k4[n4], wv = w4[n4];
+                    const float r[4] = {rv.x, rv.y, rv.z, rv.w}, k[4] = {kv4.x, kv4.y, kv4.z, kv4.w}, w[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int n = n4 * 4 + e;
-                    if (MODE == 0) {
-                        S[n] = fmaf(w[e], S[n], k[e] * vj);
-                        o = fmaf(r[e], S[n], o);
-                    } else {
-                        const float kv = k[e] * vj;
-                        o = fmaf(r[e], fmaf(U[n], kv, S[n]), o);
-                        S[n] = fmaf(w[e], S[n], kv);
+                    for (int e = 0; e < 4; ++e) {
+                        const int n = n4 * 4 + e;
+                        if (MODE == 0) {
+                            S[n] = fmaf(w[e], S[n], k[e] * vj);
+                            o = fmaf(r[e], S[n], o);
+                        } else {
+                            const float kv = k[e] * vj;
+                            o = fmaf(r[e], fmaf(U[n], kv, S[n]), o);
+                            S[n] = fmaf(w[e], S[n], kv);
+                        }
                     }
                 }
+                op[((t - s0) * kScanWarps + warp) * 32 + lane] = o;
             }
-            op[(t * kScanWarps + warp) * 32 + lane] = o;
-        }
-        __syncthreads();
-        // the chunk's reads: the warps' shares summed, float32, a row's 32 columns side by side
-        for (int t = warp; t < nt; t += kScanWarps) {
-            float sum = 0.f;
+            __syncthreads();
+            // sixteen tokens' reads: the warps' shares summed, float32, a row's 32 columns side by side
+            for (int t = warp; t < ns; t += kScanWarps) {
+                float sum = 0.f;
 #pragma unroll
-            for (int w8 = 0; w8 < kScanWarps; ++w8) sum += op[(t * kScanWarps + w8) * 32 + lane];
-            if (j < V) a.raw[(size_t)(c0 + t) * (a.H * V) + head * V + j] = sum;
+                for (int w8 = 0; w8 < kScanWarps; ++w8) sum += op[(t * kScanWarps + w8) * 32 + lane];
+                if (j < V) a.raw[(size_t)(c0 + s0 + t) * (a.H * V) + head * V + j] = sum;
+            }
+            __syncthreads();
         }
     }
 #pragma unroll
@@ -228,21 +246,37 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ raw, int H, int 
     }
 }
 
-template <int MODE, int NI>
+template <typename T, int MODE, int NI, int TC>
 static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t st) {
     const int slices = (a.V + 31) / 32;
     if (slices > 65535) return DFI_ERR_LIMIT;
-    launch(linear_scan_kernel<MODE, NI>, dim3(n_seqs, a.H, slices), dim3(kScanWarps * 32), 0, st, a);
+    constexpr int DP = kScanWarps * NI;
+    constexpr size_t bytes = sizeof(float) * (3 * TC * DP + TC * 32 + kScanTokens * kScanWarps * 32);
+    static bool raised = false;          // per instantiation
+    if (bytes > 48 * 1024 && !raised) {
+        if (cudaFuncSetAttribute(linear_scan_kernel<T, MODE, NI, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return DFI_ERR_LAUNCH;
+        }
+        raised = true;
+    }
+    launch(linear_scan_kernel<T, MODE, NI, TC>, dim3(n_seqs, a.H, slices), dim3(kScanWarps * 32), bytes, st, a);
     DFI_CHECK_LAUNCH();
     return DFI_OK;
 }
 
-template <int MODE>
-static int pick_rows(const ScanArgs& a, int n_seqs, cudaStream_t st) {
-    if (a.D <= 32) return launch_scan<MODE, 4>(a, n_seqs, st);
-    if (a.D <= 64) return launch_scan<MODE, 8>(a, n_seqs, st);
-    if (a.D <= 128) return launch_scan<MODE, 16>(a, n_seqs, st);
-    if (a.D <= 256) return launch_scan<MODE, 32>(a, n_seqs, st);
+template <typename T, int MODE, int NI>
+static int pick_fetch(const ScanArgs& a, int n_seqs, bool few_rows, cudaStream_t st) {
+    if (few_rows) return launch_scan<T, MODE, NI, kScanTokens>(a, n_seqs, st);
+    return launch_scan<T, MODE, NI, scan_fetch_tokens(NI)>(a, n_seqs, st);
+}
+
+template <typename T, int MODE>
+static int pick_rows(const ScanArgs& a, int n_seqs, bool few_rows, cudaStream_t st) {
+    if (a.D <= 32) return pick_fetch<T, MODE, 4>(a, n_seqs, few_rows, st);
+    if (a.D <= 64) return pick_fetch<T, MODE, 8>(a, n_seqs, few_rows, st);
+    if (a.D <= 128) return pick_fetch<T, MODE, 16>(a, n_seqs, few_rows, st);
+    if (a.D <= 256) return pick_fetch<T, MODE, 32>(a, n_seqs, few_rows, st);
     return DFI_ERR_LIMIT;
 }
 
@@ -276,12 +310,13 @@ __global__ void token_shift_kernel(const T* __restrict__ h, const float* __restr
 using namespace dfi;
 
 // mode 0: decay-then-read with a = sigmoid(z)^(1/decay_param); mode 1: read-then-decay with the bonus and
-// a = exp(-exp(z)).  dtype is the storage type of q, k, v, g, out and carry_rows.
+// a = exp(-exp(z)).  dtype is the storage type of q, k, v, g, out and carry_rows.  max_rows_per_seq: the most
+// rows any sequence brings (0: unknown); it only picks how many tokens a fetch covers.
 DFI_EXPORT int dfi_linear_scan(int mode, const void* q, int q_stride, const void* k, int k_stride, const void* v,
                                int v_stride, const void* g, int g_stride, const float* decay_logit,
                                const float* decay_bias, const float* bonus, float decay_param, float q_scale,
                                float* state, long long slot_stride, const int* cu_rows, const int* seq_slot,
-                               int n_seqs, int rows, int H, int D, int V, const float* norm_weight,
+                               int n_seqs, int rows, int max_rows_per_seq, int H, int D, int V, const float* norm_weight,
                                int norm_head_stride, float eps, float* raw, void* out, int out_stride,
                                float out_scale, const void* carry_rows, int carry_width, long long carry_offset,
                                int dtype, void* stream) {
@@ -302,7 +337,10 @@ DFI_EXPORT int dfi_linear_scan(int mode, const void* q, int q_stride, const void
     a.carry_rows = carry_rows; a.carry_width = carry_width; a.carry_offset = carry_offset;
     a.bf16 = dtype == DFI_DTYPE_BF16;
     cudaStream_t st = (cudaStream_t)stream;
-    int rc = mode == 0 ? pick_rows<0>(a, n_seqs, st) : mode == 1 ? pick_rows<1>(a, n_seqs, st) : DFI_ERR_SHAPE;
+    int rc = DFI_ERR_SHAPE;
+    const bool few = max_rows_per_seq > 0 && max_rows_per_seq <= kScanTokens;
+    if (mode == 0) rc = a.bf16 ? pick_rows<bf16, 0>(a, n_seqs, few, st) : pick_rows<float, 0>(a, n_seqs, few, st);
+    if (mode == 1) rc = a.bf16 ? pick_rows<bf16, 1>(a, n_seqs, few, st) : pick_rows<float, 1>(a, n_seqs, few, st);
     if (rc != DFI_OK) return rc;
     const dim3 grid(rows, (H + 3) / 4);
     if (a.bf16)

@@ -155,7 +155,9 @@ __global__ void split_decode_kernel(const T* __restrict__ q, int q_row_stride, c
     }
 }
 
-// One warp per (sequence, query head): merges the parts, applies sigmoid(gate) and out_scale.
+// One warp per (sequence, query head): merges the parts, applies sigmoid(gate) and out_scale.  Lane p first
+// works out part p's weight exp(m_p - m) (parts beyond 32 in rounds), then every lane sums its columns over
+// the parts with the loads of eight parts in flight at once.
 template <typename T>
 __global__ void split_merge_kernel(const float* __restrict__ partial, int n_q, int DV, int n_parts,
                                    const T* __restrict__ gate, int gate_row_stride, float out_scale,
@@ -165,23 +167,50 @@ __global__ void split_merge_kernel(const float* __restrict__ partial, int n_q, i
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), seq = blockIdx.x;
     if (head >= n_q) return;
-    const float* src = partial + ((size_t)seq * n_q + head) * n_parts * (size_t)(2 + DV);
+    const size_t stride = (size_t)(2 + DV);
+    const float* src = partial + ((size_t)seq * n_q + head) * n_parts * stride;
     float m = -INFINITY;
-    for (int p = 0; p < n_parts; ++p) m = fmaxf(m, src[(size_t)p * (2 + DV)]);
+    for (int p = lane; p < n_parts; p += 32) m = fmaxf(m, src[p * stride]);
+    m = warp_max(m);
     float l = 0.f;
-    for (int p = 0; p < n_parts; ++p) {
-        const float mp = src[(size_t)p * (2 + DV)];
-        if (mp != -INFINITY) l += src[(size_t)p * (2 + DV) + 1] * expf(mp - m);
+    for (int p = lane; p < n_parts; p += 32) {
+        const float mp = src[p * stride];
+        if (mp != -INFINITY) l += src[p * stride + 1] * expf(mp - m);
     }
+    l = warp_sum(l);
     float factor = out_scale / l;
     if (gate != nullptr) factor /= 1.f + expf(-to_float(gate[(size_t)seq * gate_row_stride + head]));
-    for (int d = lane; d < DV; d += 32) {
-        float v = 0.f;
-        for (int p = 0; p < n_parts; ++p) {
-            const float mp = src[(size_t)p * (2 + DV)];
-            if (mp != -INFINITY) v += src[(size_t)p * (2 + DV) + 2 + d] * expf(mp - m);
+    float acc[8];                                    // columns lane, lane + 32, ... (DV <= 256)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int p0 = 0; p0 < n_parts; p0 += 32) {
+        const int mine = p0 + lane;
+        const float mp = mine < n_parts ? src[mine * stride] : -INFINITY;
+        const float weight = mp == -INFINITY ? 0.f : expf(mp - m);
+        const int count = min(32, n_parts - p0);
+        // every load is issued whatever its index (clamped): a straight run of loads whose latencies overlap;
+        // a part or a column that does not exist gets the weight 0
+        const int n_cols = (DV + 31) >> 5;
+        for (int pp = 0; pp < 32; pp += 4) {
+            if (pp >= count) break;
+            float c[4], x[4][8];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                c[u] = pp + u < count ? __shfl_sync(0xffffffffu, weight, (pp + u) & 31) : 0.f;
+                const float* row = src + (size_t)(p0 + min(pp + u, count - 1)) * stride + 2;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[u][j] = j < n_cols ? __ldg(row + min(lane + 32 * j, DV - 1)) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = fmaf(c[u], x[u][j], acc[j]);
         }
-        out[(size_t)seq * out_row_stride + (size_t)head * DV + d] = from_float<T>(v * factor);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int d = lane + 32 * j;
+        if (d < DV) out[(size_t)seq * out_row_stride + (size_t)head * DV + d] = from_float<T>(acc[j] * factor);
     }
 }
 
