@@ -10,8 +10,8 @@
 // reads are float32 whatever the storage type of q, k, v; the recurrence runs in the order of the tokens,
 // so a prompt taken whole, in portions or token by token gives the same state up to nothing at all.
 //
-// One CTA of eight warps owns one (sequence, head, 32 columns of S) for all the tokens the step brings
-// it: a column of S needs no other column, so a head spreads over V / 32 CTAs.  Warp w keeps rows
+// One CTA of eight warps owns one (sequence, head, 32 or 16 columns of S) for all the tokens the step brings
+// it: a column of S needs no other column, so a head spreads over V / 32 (or V / 16) CTAs.  Warp w keeps rows
 // [w NI, (w+1) NI) of its columns in registers, lane c column c.  Tokens are fetched up to 64 at a time: their
 // q, k, decays and v wait in shared memory as float32 (the decay computed once per token and channel), and
 // while they are worked through the next ones are already on their way from global memory into registers:
@@ -80,9 +80,9 @@ __device__ __forceinline__ float decay_of(float z, float param) {
 __host__ __device__ constexpr int scan_fetch_tokens(int ni) { return ni <= 16 ? 32 : 16; }
 
 // What a thread fetches for the chunk of up to TC tokens at row c0: elements tid, tid + THREADS, ... of
-// [TC][DP] (q, k, decay logits) and of [TC][32] (v); zeros past the chunk's tokens and the head's sizes.
-template <typename T, int TC, int DP, int PER, int PER_V>
-__device__ __forceinline__ void scan_fetch(const ScanArgs& a, int c0, int row1, int head, int j, int tid,
+// [TC][DP] (q, k, decay logits) and of [TC][COLS] (v, the CTA's columns from col0 on).
+template <typename T, int TC, int DP, int COLS, int PER, int PER_V>
+__device__ __forceinline__ void scan_fetch(const ScanArgs& a, int c0, int row1, int head, int col0, int tid,
                                            T (&fq)[PER], T (&fk)[PER], float (&fz)[PER], T (&fv)[PER_V]) {
     // Every load is issued whatever its index (clamped into the chunk and the head) and nothing is done with
     // its value here: one straight run of loads, whose latencies overlap; what lies outside is set to zero
@@ -103,22 +103,28 @@ __device__ __forceinline__ void scan_fetch(const ScanArgs& a, int c0, int row1, 
     }
 #pragma unroll
     for (int e = 0; e < PER_V; ++e) {
-        const int idx = tid + e * THREADS, t = min(idx >> 5, last);
-        fv[e] = __ldg(v + (size_t)(c0 + t) * a.v_stride + head * V + min(j, V - 1));
+        const int idx = tid + e * THREADS, t = min(idx / COLS, last);
+        fv[e] = __ldg(v + (size_t)(c0 + t) * a.v_stride + head * V + min(col0 + idx % COLS, V - 1));
     }
 }
 
-template <typename T, int MODE, int NI, int TC>
+// COLS: columns of S per CTA, 32 (a lane a column) or 16: then the two halves of a warp share the columns and
+// split the warp's rows, their shares of o_t meet by one shuffle, and a head spreads over twice the CTAs (for
+// steps with fewer (sequence, head, 32 columns) than SMs).
+template <typename T, int MODE, int NI, int TC, int COLS>
 __global__ void __launch_bounds__(kScanWarps * 32, (NI <= 8 ? 2 : 1)) linear_scan_kernel(const ScanArgs a) {
     constexpr int DP = kScanWarps * NI, THREADS = kScanWarps * 32;
+    constexpr int NIL = NI * COLS / 32;               // rows of S a lane keeps
+    static_assert(NIL % 4 == 0, "a lane's rows come in fours");
     constexpr int PER = TC * DP / THREADS;            // elements of q, k, z a thread fetches per chunk
-    constexpr int PER_V = TC * 32 / THREADS;          // and of v
+    constexpr int PER_V = TC * COLS / THREADS;        // and of v
+    static_assert(PER_V >= 1, "every thread fetches a value");
     extern __shared__ __align__(16) float smem[];
     float* rs = smem;                                 // [TC][DP]
     float* ks = rs + TC * DP;                         // [TC][DP]
     float* ws = ks + TC * DP;                         // [TC][DP]
-    float* vs = ws + TC * DP;                         // [TC][32]
-    float* op = vs + TC * 32;                         // [kScanTokens][warps][32]
+    float* vs = ws + TC * DP;                         // [TC][COLS]
+    float* op = vs + TC * COLS;                       // [kScanTokens][warps][COLS]
     pdl_launch_next();
     pdl_wait();
     const int seq = blockIdx.x, head = blockIdx.y;
@@ -126,13 +132,14 @@ __global__ void __launch_bounds__(kScanWarps * 32, (NI <= 8 ? 2 : 1)) linear_sca
     if (row1 <= row0) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int D = a.D, V = a.V;
-    const int j = blockIdx.z * 32 + lane;             // this lane's column of S
+    const int col0 = blockIdx.z * COLS, cl = lane % COLS;
+    const int j = col0 + cl;                          // this lane's column of S
     float* S_g = a.state + (size_t)a.seq_slot[seq] * a.slot_stride + (size_t)head * D * V;
-    const int i0 = warp * NI;
+    const int i0 = warp * NI + (lane / COLS) * NIL;   // and the first of its rows
 
-    float S[NI], U[NI];
+    float S[NIL], U[NIL];
 #pragma unroll
-    for (int n = 0; n < NI; ++n) {
+    for (int n = 0; n < NIL; ++n) {
         const int i = i0 + n;
         U[n] = (MODE == 1 && i < D) ? a.bonus[head * D + i] : 0.f;
         S[n] = (i < D && j < V) ? S_g[(size_t)i * V + j] : 0.f;
@@ -147,7 +154,7 @@ __global__ void __launch_bounds__(kScanWarps * 32, (NI <= 8 ? 2 : 1)) linear_sca
         bias[e] = (a.decay_bias != nullptr && i < D) ? a.decay_bias[head * D + i] : 0.f;
     }
 
-    scan_fetch<T, TC, DP, PER, PER_V>(a, row0, row1, head, j, tid, fq, fk, fz, fv);
+    scan_fetch<T, TC, DP, COLS, PER, PER_V>(a, row0, row1, head, col0, tid, fq, fk, fz, fv);
     for (int c0 = row0; c0 < row1; c0 += TC) {
         const int nt = min(TC, row1 - c0);
         __syncthreads();                               // the chunk before is done with shared memory
@@ -162,22 +169,22 @@ __global__ void __launch_bounds__(kScanWarps * 32, (NI <= 8 ? 2 : 1)) linear_sca
 #pragma unroll
         for (int e = 0; e < PER_V; ++e) {
             const int idx = tid + e * THREADS;
-            vs[idx] = (j < V && (idx >> 5) < nt) ? to_float(fv[e]) : 0.f;
+            vs[idx] = (col0 + idx % COLS < V && idx / COLS < nt) ? to_float(fv[e]) : 0.f;
         }
         __syncthreads();
         if (c0 + TC < row1)                            // on its way while this chunk is worked through
-            scan_fetch<T, TC, DP, PER, PER_V>(a, c0 + TC, row1, head, j, tid, fq, fk, fz, fv);
+            scan_fetch<T, TC, DP, COLS, PER, PER_V>(a, c0 + TC, row1, head, col0, tid, fq, fk, fz, fv);
         for (int s0 = 0; s0 < nt; s0 += kScanTokens) {
             const int ns = min(kScanTokens, nt - s0);
 #pragma unroll 2
             for (int t = s0; t < s0 + ns; ++t) {
-                const float vj = vs[t * 32 + lane];
+                const float vj = vs[t * COLS + cl];
                 float o = 0.f;
                 const float4* r4 = reinterpret_cast<const float4*>(rs + t * DP + i0);
                 const float4* k4 = reinterpret_cast<const float4*>(ks + t * DP + i0);
                 const float4* w4 = reinterpret_cast<const float4*>(ws + t * DP + i0);
 #pragma unroll
-                for (int n4 = 0; n4 < NI / 4; ++n4) {
+                for (int n4 = 0; n4 < NIL / 4; ++n4) {
                     const float4 rv = r4[n4], kv4 = k4[n4], wv = w4[n4];
                     const float r[4] = {rv.x, rv.y, rv.z, rv.w}, k[4] = {kv4.x, kv4.y, kv4.z, kv4.w}, w[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
@@ -193,21 +200,22 @@ __global__ void __launch_bounds__(kScanWarps * 32, (NI <= 8 ? 2 : 1)) linear_sca
                         }
                     }
                 }
-                op[((t - s0) * kScanWarps + warp) * 32 + lane] = o;
+                if (COLS < 32) o += __shfl_xor_sync(0xffffffffu, o, COLS);
+                if (lane < COLS) op[((t - s0) * kScanWarps + warp) * COLS + lane] = o;
             }
             __syncthreads();
             // sixteen tokens' reads: the warps' shares summed, float32, a row's 32 columns side by side
             for (int t = warp; t < ns; t += kScanWarps) {
                 float sum = 0.f;
 #pragma unroll
-                for (int w8 = 0; w8 < kScanWarps; ++w8) sum += op[(t * kScanWarps + w8) * 32 + lane];
-                if (j < V) a.raw[(size_t)(c0 + s0 + t) * (a.H * V) + head * V + j] = sum;
+                for (int w8 = 0; w8 < kScanWarps; ++w8) sum += op[(t * kScanWarps + w8) * COLS + cl];
+                if (lane < COLS && j < V) a.raw[(size_t)(c0 + s0 + t) * (a.H * V) + head * V + j] = sum;
             }
             __syncthreads();
         }
     }
 #pragma unroll
-    for (int n = 0; n < NI; ++n) {
+    for (int n = 0; n < NIL; ++n) {
         const int i = i0 + n;
         if (i < D && j < V) S_g[(size_t)i * V + j] = S[n];
     }
@@ -246,29 +254,52 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ raw, int H, int 
     }
 }
 
-template <typename T, int MODE, int NI, int TC>
+template <typename T, int MODE, int NI, int TC, int COLS>
 static int launch_scan(const ScanArgs& a, int n_seqs, cudaStream_t st) {
-    const int slices = (a.V + 31) / 32;
+    const int slices = (a.V + COLS - 1) / COLS;
     if (slices > 65535) return DFI_ERR_LIMIT;
     constexpr int DP = kScanWarps * NI;
-    constexpr size_t bytes = sizeof(float) * (3 * TC * DP + TC * 32 + kScanTokens * kScanWarps * 32);
+    constexpr size_t bytes = sizeof(float) * (3 * TC * DP + TC * COLS + kScanTokens * kScanWarps * COLS);
     static bool raised = false;          // per instantiation
     if (bytes > 48 * 1024 && !raised) {
-        if (cudaFuncSetAttribute(linear_scan_kernel<T, MODE, NI, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) {
+        if (cudaFuncSetAttribute(linear_scan_kernel<T, MODE, NI, TC, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) {
             cudaGetLastError();
             return DFI_ERR_LAUNCH;
         }
         raised = true;
     }
-    launch(linear_scan_kernel<T, MODE, NI, TC>, dim3(n_seqs, a.H, slices), dim3(kScanWarps * 32), bytes, st, a);
+    launch(linear_scan_kernel<T, MODE, NI, TC, COLS>, dim3(n_seqs, a.H, slices), dim3(kScanWarps * 32), bytes, st, a);
     DFI_CHECK_LAUNCH();
     return DFI_OK;
 }
 
+static int sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) {
+            cudaGetLastError();
+            count = 148;
+        }
+    }
+    return count;
+}
+
 template <typename T, int MODE, int NI>
 static int pick_fetch(const ScanArgs& a, int n_seqs, bool few_rows, cudaStream_t st) {
-    if (few_rows) return launch_scan<T, MODE, NI, kScanTokens>(a, n_seqs, st);
-    return launch_scan<T, MODE, NI, scan_fetch_tokens(NI)>(a, n_seqs, st);
+    // so few (sequence, head, 32 columns) that twice as many still find an SM each: 16 columns a CTA (a token
+    // costs a CTA about the same either way: what it waits for is the chain through one token's sum, so a
+    // second CTA on an SM would only double that SM's time; measured at 40 heads of 64 x 64, one sequence:
+    // 80 CTAs of 32 columns 296 us for 2,048 tokens, 160 CTAs of 16 columns on 148 SMs 338 us)
+    if constexpr (NI >= 8) {
+        if (2LL * n_seqs * a.H * ((a.V + 31) / 32) <= sm_count()) {
+            if (few_rows) return launch_scan<T, MODE, NI, kScanTokens, 16>(a, n_seqs, st);
+            return launch_scan<T, MODE, NI, scan_fetch_tokens(NI), 16>(a, n_seqs, st);
+        }
+    }
+    if (few_rows) return launch_scan<T, MODE, NI, kScanTokens, 32>(a, n_seqs, st);
+    return launch_scan<T, MODE, NI, scan_fetch_tokens(NI), 32>(a, n_seqs, st);
 }
 
 template <typename T, int MODE>

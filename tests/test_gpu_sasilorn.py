@@ -120,7 +120,7 @@ def test_dynamic_tanh_and_activations(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("mode", ["decay_then_read", "read_then_decay"])
-@pytest.mark.parametrize("heads, dim, vdim", [(2, 16, 8), (1, 24, 40), (3, 64, 64), (2, 100, 70), (1, 130, 33)])
+@pytest.mark.parametrize("heads, dim, vdim", [(2, 16, 8), (1, 24, 40), (3, 64, 64), (2, 100, 70), (1, 130, 33), (20, 64, 96)])
 def test_linear_scan_whole_in_portions_and_in_another_slot(mode, heads, dim, vdim, dtype):
     """The recurrence over packed rows of three sequences against the token-by-token loop, then the same
     rows cut into portions (16 is the kernel's own chunk: 15, 16, 17 sit around its edge)."""
