@@ -67,7 +67,11 @@ class SasilornConfig(ModelConfig):
 
     def source_of(self, index: int) -> int:
         """The layer whose tensors layer ``index`` runs (itself unless it says ``weights_of``)."""
-        return self.layers[index].get("weights_of", index)
+        seen = set()
+        while "weights_of" in self.layers[index] and index not in seen:
+            seen.add(index)
+            index = self.layers[index]["weights_of"]
+        return index
 
     def validate(self) -> None:
         if self.vocab_size <= 0 or self.hidden_size <= 0:
@@ -104,9 +108,9 @@ class SasilornConfig(ModelConfig):
             source = layer.get("weights_of")
             if source is not None:
                 if isinstance(source, bool) or not isinstance(source, int) or not 0 <= source < len(self.layers) \
-                        or source == index or "weights_of" in self.layers[source]:
+                        or source == index or "weights_of" in self.layers[self.source_of(index)]:
                     raise ConfigError(f"config.json: {where}.weights_of must name another layer that has tensors of its own")
-                other = self.layers[source]
+                other = self.layers[self.source_of(index)]
                 if other.get("type") != layer["type"] or (other.get("mlp") is None) != (mlp is None):
                     raise ConfigError(f"config.json: {where} runs layer {source}'s tensors but is of another kind")
 

@@ -43,7 +43,15 @@ CASE_B = {"architecture": "Sasilorn", "vocab": 75, "width": 72, "norm": {"eps": 
 #: no layer keeps keys and values; a width that is no multiple of 8
 CASE_C = {"architecture": "Sasilorn", "vocab": 50, "width": 44, "norm": {"eps": 1e-5}, "layers": [
     _wkv(2, 16, 60), _wkv(1, 40, 0)]}
-CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C}
+#: sizes in steps of 16, which the bfloat16 engine runs on its tensor-core attention, and heads of 64 key channels
+CASE_D = {"architecture": "Sasilorn", "vocab": 120, "width": 128, "norm": {"eps": 1e-5}, "layers": [
+    _parallel({"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 64, "scale": 0.2},
+              {"heads": 2, "dim": 64, "vdim": 32, "tau": 16.0}, 0.8, 0.9, 160),
+    _wkv(2, 64, 0),
+    _parallel({"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 64, "scale": 0.2},
+              {"heads": 2, "dim": 64, "vdim": 32, "tau": 16.0}, 0.8, 0.9, 160, weights_of=0),
+]}
+CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D}
 
 
 def one_layer(kind: str) -> dict:

@@ -211,7 +211,7 @@ def test_token_shift_reads_the_row_before_or_the_kept_one(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("n_q, n_kv, dim, vdim", [(4, 2, 16, 24), (3, 3, 20, 12), (4, 1, 8, 36), (8, 2, 48, 80),
+@pytest.mark.parametrize("n_q, n_kv, dim, vdim", [(4, 2, 16, 24), (3, 3, 20, 12), (4, 1, 8, 36), (8, 4, 96, 48),
                                                   (6, 2, 32, 64), (2, 1, 128, 128), (2, 2, 256, 16)])
 def test_attention_with_values_of_their_own_size(n_q, n_kv, dim, vdim, dtype):
     """Norm and cache write, then every row's attention over scrambled pages: prompt rows by the row kernel
@@ -361,13 +361,14 @@ def test_unequal_batches_and_slots_used_again(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_far_keys_page_borders_and_long_memory(tmp_path, dtype):
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_far_keys_page_borders_and_long_memory(tmp_path, name, dtype):
     """Sharp attention (scores six times larger: the softmax rests on a few keys, wherever they are) and
     decays close to 1 (tokens hundreds of places back still count): the last tokens of a long prompt, read
     whole, after portions that end on and beside page borders, and token by token across a border."""
     from dryft_flash_infer_b200 import StepEntry
 
-    folder, config, tensors = make(tmp_path, sharpened(CASES["A"]), seed=23, change=long_memory)
+    folder, config, tensors = make(tmp_path, sharpened(CASES[name]), seed=23, change=long_memory)
     prompt = prompts(config, [400], seed=9)[0]
     want = plain_logits(config, tensors, prompt)
     # the far tokens do matter: without the first 300, the last logits are other logits
