@@ -267,10 +267,10 @@ def sasilorn_config(width: int, layers: int, vocab: int) -> dict:
     wkv = {"type": "wkv", "mixer": {"heads": width // 64, "dim": 64, "rank": 64}}
     wkv["mlp"] = {"kind": "dense", "ff": (budget - 5 * width * width) // (2 * width) // 64 * 64}
     left = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
-    right = {"heads": heads // 2, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 64}
+    right = {"heads": heads // 2, "dim": 64, "vdim": 128, "tau": 12.0, "rank": 64}
     mixer_weights = width * ((left["heads"] + left["kv_heads"]) * 128 + left["kv_heads"] * 128 + left["heads"] * 128) \
         + width * right["heads"] * (2 * 64 + 3 * 128)
-    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 0.9},
+    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.75, "right_scale": 1.0},
            "mlp": {"kind": "dense", "ff": (budget - mixer_weights) // (2 * width) // 64 * 64}}
     return {"architecture": "Sasilorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "layers": [wkv if i % 2 == 0 else par for i in range(layers)]}

@@ -20,7 +20,7 @@ from typing import Any, ClassVar
 from .base import ConfigError, ModelConfig, take
 
 MIXER_TYPES = ("wkv", "parallel")
-DEFAULT_RANK = 16
+DEFAULT_RANK = 32
 
 
 def _positive(raw: dict, key: str, where: str) -> int:

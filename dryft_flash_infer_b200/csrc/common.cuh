@@ -93,6 +93,17 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return warp_sum(total);
 }
 
+// Element-wise activations by code: 0 relu(x)^2, 1 gelu in its tanh form, 2 silu, 3 relu, 4 tanh.
+__device__ __forceinline__ float activate(float z, int kind) {
+    switch (kind) {
+        case 0: { const float r = fmaxf(z, 0.f); return r * r; }
+        case 1: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        case 2: return z / (1.f + expf(-z));
+        case 3: return fmaxf(z, 0.f);
+        default: return tanhf(z);
+    }
+}
+
 // Programmatic dependent launch: a kernel launched through `launch` may begin while the kernel
 // before it on the stream is still running; it must call pdl_wait() before it reads anything an
 // earlier kernel wrote (or writes anything an earlier kernel reads), and may do work that depends

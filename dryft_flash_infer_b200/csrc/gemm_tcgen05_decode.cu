@@ -68,6 +68,7 @@ struct RowFusion {
     bf16* residual;           // add-norm output: [M, N] updated in place, or null
     const float* norm_weight; // [N]
     float* out_ssq;           // [row_blocks][kSsqStride]
+    int act;                  // 0: none; else 1 + the code of `activate`, applied to the sums of a plain product
 };
 
 // First unit of a CTA's run.  Two ways of dealing the units out: equal contiguous runs over the
@@ -180,6 +181,9 @@ __device__ __forceinline__ void finish_group(const RowFusion& fusion, const Stre
     if (SWIGLU) {
         v.x = silu_times(v.x, u.x); v.y = silu_times(v.y, u.y);
         v.z = silu_times(v.z, u.z); v.w = silu_times(v.w, u.w);
+    } else if (fusion.act != 0) {
+        v.x = activate(v.x, fusion.act - 1); v.y = activate(v.y, fusion.act - 1);
+        v.z = activate(v.z, fusion.act - 1); v.w = activate(v.w, fusion.act - 1);
     }
     const float vals[4] = {v.x, v.y, v.z, v.w};
     if (!SWIGLU && fusion.residual != nullptr) {
@@ -827,4 +831,14 @@ DFI_EXPORT int dfi_gemm_decode_fused(const void* x, const void* w, void* out, in
         fusion.out_ssq = out_ssq;
     }
     return gemm_decode(x, w, out, M, N, K, swiglu, n_ctas, partials, counters, out_dtype, fusion, next_hint, stream);
+}
+
+// The plain product followed by an element-wise activation on the float32 sums (`act`: a code of `activate`
+// in common.cuh), rounded once: the first half of a feed-forward without a gate.
+DFI_EXPORT int dfi_gemm_decode_act(const void* x, const void* w, void* out, int M, int N, int K, int act, int n_ctas,
+                                   float* partials, int* counters, int out_dtype, const void* next_hint, void* stream) {
+    if (act < 0 || act > 4) return DFI_ERR_SHAPE;
+    RowFusion fusion = {};
+    fusion.act = act + 1;
+    return gemm_decode(x, w, out, M, N, K, 0, n_ctas, partials, counters, out_dtype, fusion, next_hint, stream);
 }

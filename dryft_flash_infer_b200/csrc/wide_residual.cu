@@ -69,18 +69,7 @@ __global__ void add_to_float_kernel(float* __restrict__ residual, const T* __res
         residual[i] += to_float(delta[i]);
 }
 
-// Activations of a dense feed-forward, in place on its inner rows.
-// 0: relu(x)^2   1: gelu with the tanh form   2: silu   3: relu   4: tanh
-__device__ __forceinline__ float activate(float z, int kind) {
-    switch (kind) {
-        case 0: { const float r = fmaxf(z, 0.f); return r * r; }
-        case 1: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-        case 2: return z / (1.f + expf(-z));
-        case 3: return fmaxf(z, 0.f);
-        default: return tanhf(z);
-    }
-}
-
+// Activations of a dense feed-forward, in place on its inner rows (`activate` of common.cuh).
 template <typename T>
 __global__ void activation_kernel(T* __restrict__ x, long long n, int kind) {
     pdl_launch_next();

@@ -992,6 +992,29 @@ def decode_linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
     return out
 
 
+def linear_act(x: torch.Tensor, weight: torch.Tensor, kind: str, then: NextWeights | None = None) -> torch.Tensor:
+    """``act(x @ weight.T)`` for ``kind`` in ``ACTIVATIONS``: for at most 64 bfloat16 rows the decode product
+    applies the activation to its float32 sums before the one rounding; otherwise the product, then
+    ``activation`` in place."""
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {kind!r}; known: {', '.join(ACTIVATIONS)}")
+    if (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+            and weight.is_contiguous() and x.shape[0] <= SKINNY_MAX_ROWS and x.shape[1] % 8 == 0
+            and x.shape[1] == weight.shape[1] and x.data_ptr() % 16 == 0):
+        m, k = x.shape
+        n = weight.shape[0]
+        lib = _core()
+        n_ctas = lib.dfi_sm_count()
+        lib.dfi_gemm_decode_partial_floats.restype = ctypes.c_longlong
+        held = _scratch(_DECODE_SCRATCH, x.device, lib.dfi_gemm_decode_partial_floats(n_ctas), lib.dfi_gemm_decode_counters(n, 0))
+        out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+        _check(lib.dfi_gemm_decode_act(_ptr(x), _ptr(weight), _ptr(out), m, n, k, ACTIVATIONS[kind], n_ctas, _ptr(held[0]),
+                                       _ptr(held[1]), _DTYPE_CODE[x.dtype], _hint(then, m), _stream()), "linear_act",
+               f"{m} x {k} by {n} x {k}")
+        return out
+    return activation(linear(x, weight, then=then), kind)
+
+
 def simt_linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """``x @ weight.T`` on the float32 pipes (``csrc/gemm_simt.cu``): every product and sum in float32 in
     the order of k.  Any sizes; float32 operands, or bfloat16 ones with a bfloat16 or float32 result."""

@@ -142,8 +142,7 @@ class TimeMix(Mixer):
         k = kernels.linear(blends[1], self.k, then=kernels.next_weights(self.v))
         v = kernels.linear(blends[2], self.v, then=kernels.next_weights(self.g))
         g = kernels.linear(blends[3], self.g)
-        narrow = kernels.linear(blends[4], self.w1)
-        kernels.activation(narrow, "tanh")
+        narrow = kernels.linear_act(blends[4], self.w1, "tanh")
         z = kernels.linear(narrow, self.w2, out_dtype=torch.float32)
         if out is None:
             out = torch.empty((x.shape[0], hv), dtype=x.dtype, device=x.device)

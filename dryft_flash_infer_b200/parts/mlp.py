@@ -67,8 +67,7 @@ class DenseMLP(FeedForward):
         return kernels.next_weights(self.up)
 
     def forward(self, x, ctx, add_norm=None):
-        inner = kernels.linear(x, self.up, then=kernels.next_weights(self.down))
-        kernels.activation(inner, self.activation)
+        inner = kernels.linear_act(x, self.up, self.activation, then=kernels.next_weights(self.down))
         return kernels.linear(inner, self.down, then=getattr(ctx, "upcoming", None))
 
 

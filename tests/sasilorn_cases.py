@@ -46,10 +46,10 @@ CASE_C = {"architecture": "Sasilorn", "vocab": 50, "width": 44, "norm": {"eps": 
 #: sizes in steps of 16, which the bfloat16 engine runs on its tensor-core attention, and heads of 64 key channels
 CASE_D = {"architecture": "Sasilorn", "vocab": 120, "width": 128, "norm": {"eps": 1e-5}, "layers": [
     _parallel({"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 64, "scale": 0.2},
-              {"heads": 2, "dim": 64, "vdim": 32, "tau": 16.0}, 0.8, 0.9, 160),
+              {"heads": 2, "dim": 64, "vdim": 32, "tau": 12.0}, 0.75, 1.25, 160),
     _wkv(2, 64, 0),
     _parallel({"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 64, "scale": 0.2},
-              {"heads": 2, "dim": 64, "vdim": 32, "tau": 16.0}, 0.8, 0.9, 160, weights_of=0),
+              {"heads": 2, "dim": 64, "vdim": 32, "tau": 12.0}, 0.75, 1.25, 160, weights_of=0),
 ]}
 CASES = {"A": CASE_A, "B": CASE_B, "C": CASE_C, "D": CASE_D}
 

@@ -118,6 +118,24 @@ def test_dynamic_tanh_and_activations(dtype):
             assert (got - want.float()).abs().max() <= (1e-5 if dtype == torch.float32 else 0.05 * (1 + want.abs().max())), kind
 
 
+@pytest.mark.parametrize("rows", [1, 8, 33, 64, 200])
+@pytest.mark.parametrize("kind", ["relu2", "tanh", "gelu_tanh", "silu", "relu"])
+def test_product_with_an_activation_on_its_sums(rows, kind):
+    """Up to 64 bfloat16 rows: the activation in the decode product's epilogue, on the float32 sums; more rows
+    (and float32): the product, then the activation kernel."""
+    from dryft_flash_infer_b200.ops import kernels
+
+    torch.manual_seed(rows)
+    x, w = (torch.randn(rows, 96) * 0.5).to(torch.bfloat16), (torch.randn(200, 96) * 0.2).to(torch.bfloat16)
+    z = x.double() @ w.double().T
+    want = {"relu2": torch.relu(z) ** 2, "silu": z * torch.sigmoid(z), "relu": torch.relu(z), "tanh": torch.tanh(z),
+            "gelu_tanh": 0.5 * z * (1 + torch.tanh((2 / torch.pi) ** 0.5 * (z + 0.044715 * z ** 3)))}[kind]
+    got = kernels.linear_act(x.cuda(), w.cuda(), kind).float().cpu()
+    assert (got - want.float()).abs().max() <= 0.02 * (1 + want.abs().max())
+    got32 = kernels.linear_act(x.float().cuda(), w.float().cuda(), kind).cpu()
+    assert (got32 - want.float()).abs().max() <= 1e-4 * (1 + want.abs().max())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("mode", ["decay_then_read", "read_then_decay"])
 @pytest.mark.parametrize("heads, dim, vdim", [(2, 16, 8), (1, 24, 40), (3, 64, 64), (2, 100, 70), (1, 130, 33), (20, 64, 96)])
